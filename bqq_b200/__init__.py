@@ -1,0 +1,17 @@
+"""bqq_b200: B200 (sm_100a) implementation of the BinaryQuadratic linear forward.
+
+`bqq_b200.bqq_modules` mirrors the reference module of the same name; `install()`
+registers it as the top-level module `bqq_modules` so that pickled models that
+record `bqq_modules.BinaryQuadratic` load onto this implementation.
+"""
+import sys
+
+from . import _cabi  # noqa: F401  (fails loudly when the CUDA library is missing)
+from . import bqq_modules
+from .bqq_modules import (BinaryQuadratic, PackedBinaryQuadratic, get_matrices,  # noqa: F401
+                          pack_binaryquadratic_model, replace_linear_with_bqq, shard_rows)
+
+
+def install() -> None:
+    """Make `import bqq_modules` / unpickling resolve to this package's module."""
+    sys.modules['bqq_modules'] = bqq_modules

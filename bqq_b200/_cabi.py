@@ -1,0 +1,87 @@
+"""ctypes binding of libbqq_b200.so (the C ABI declared in include/bqq_b200.h).
+
+The library is built in-tree by bqq_b200/build.py.  There is no fallback: if the
+shared object is missing, importing this module raises, and every wrapper turns a
+non-zero return code into RuntimeError(bqq_strerror(rc)).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, 'libbqq_b200.so')
+
+F32, BF16, F16 = 0, 1, 2
+DECODE_MAX_M = 16
+
+EXPORTS = [
+    'bqq_abi_version', 'bqq_strerror', 'bqq_device_supported',
+    'bqq_zplane_words', 'bqq_yplane_words', 'bqq_coeff_floats', 'bqq_algorithmic_bytes',
+    'bqq_pack_planes', 'bqq_unpack_planes', 'bqq_pack_planes_host', 'bqq_unpack_planes_host',
+    'bqq_repack_u8_planes', 'bqq_pack_coeffs',
+    'bqq_decode_workspace_bytes', 'bqq_forward_decode',
+    'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
+    'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
+]
+
+
+class BqqDims(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ('bw', 'rw', 'cw', 'P', 'Q', 'r')]
+
+
+class BqqLayer(C.Structure):
+    _fields_ = [('dims', BqqDims), ('zplanes', C.c_void_p), ('yplanes', C.c_void_p),
+                ('coef', C.c_void_p), ('bias', C.c_void_p), ('bias_dtype', C.c_int32),
+                ('reserved', C.c_int32)]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f'{LIB_PATH} is missing: build it with `python -m bqq_b200.build` '
+            '(needs nvcc); bqq_b200 has no fallback path')
+    lib = C.CDLL(LIB_PATH)
+    vp, i32, i64, sz, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_float
+    dp, lp = C.POINTER(BqqDims), C.POINTER(BqqLayer)
+    sig = {
+        'bqq_abi_version': (C.c_int, []),
+        'bqq_strerror': (C.c_char_p, [i32]),
+        'bqq_device_supported': (C.c_int, []),
+        'bqq_zplane_words': (sz, [dp]), 'bqq_yplane_words': (sz, [dp]),
+        'bqq_coeff_floats': (sz, [dp]), 'bqq_algorithmic_bytes': (sz, [dp]),
+        'bqq_pack_planes': (i32, [vp, vp, dp, vp, vp, vp, vp, vp]),
+        'bqq_unpack_planes': (i32, [vp, vp, dp, vp, vp, vp]),
+        'bqq_pack_planes_host': (i32, [vp, vp, dp, vp, vp, vp, vp]),
+        'bqq_unpack_planes_host': (i32, [vp, vp, dp, vp, vp]),
+        'bqq_repack_u8_planes': (i32, [vp, vp, dp, vp, vp, vp]),
+        'bqq_pack_coeffs': (i32, [vp, vp, vp, vp, i32, dp, vp, vp]),
+        'bqq_decode_workspace_bytes': (sz, [dp, i32]),
+        'bqq_prefill_workspace_bytes': (sz, [dp, i32]),
+        'bqq_forward_workspace_bytes': (sz, [dp, i32]),
+        'bqq_forward_decode': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
+        'bqq_forward_prefill': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
+        'bqq_forward': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
+        'bqq_reconstruct_weight': (i32, [lp, vp, i32, f32, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def strerror(rc: int) -> str:
+    return lib.bqq_strerror(rc).decode()
+
+
+def check(rc: int, what: str = 'bqq call') -> None:
+    if rc != 0:
+        raise RuntimeError(f'{what} failed: {strerror(rc)} (code {rc})')
+
+
+def dims(bw, rw, cw, P, Q, r) -> BqqDims:
+    return BqqDims(int(bw), int(rw), int(cw), int(P), int(Q), int(r))

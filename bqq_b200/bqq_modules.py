@@ -1,0 +1,405 @@
+"""Drop-in `bqq_modules` for the B200 path.
+
+Same names, constructor arguments, attributes and state_dict layout as the
+reference module neural_network_compression/src/bqq_modules.py, so that
+saved whole-model pickles (which record the class path
+`bqq_modules.BinaryQuadratic`), `replace_linear_with_bqq`
+(lm/build_bqq_model.py:79-112) and the `__new__`-and-fill construction of
+lm/benchmark_inference.py:24-41 keep working.  Put this package's directory on
+sys.path in place of the reference's `src/`, or call `bqq_b200.install()`.
+
+What differs is only how forward() computes: instead of rebuilding the dense
+weight with torch ops on every call (src/bqq_modules.py:34-46) it calls the
+C-ABI CUDA library through ctypes.  There is no Triton path, no backend switch
+and no CPU fallback: a module whose buffers are not on an sm_100 GPU raises.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import _cabi
+from ._cabi import BqqLayer, check, lib
+
+_DTYPE_CODE = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
+
+
+# ---------------------------------------------------------------------------
+# workspace cache: one growing buffer per (device, stream, kind)
+# ---------------------------------------------------------------------------
+_WORKSPACES: dict = {}
+
+
+def _workspace(device: torch.device, kind: str, nbytes: int) -> torch.Tensor:
+    """Scratch buffer for the kernels.  Decode scratch must start zeroed (the
+    kernel leaves it zeroed); calls that share a buffer must not overlap on the
+    GPU, hence one buffer per stream."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream, kind)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(int(nbytes), 256)
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+class _PackedState:
+    """Derived, non-persistent device state of one layer: bit planes, row sums
+    and fp32 coefficient records, rebuilt when the source tensors change."""
+
+    __slots__ = ('plane_key', 'coef_key', 'dims', 'zplanes', 'yplanes', 'ysum', 'zsum', 'coef',
+                 'bias_key', 'layer')
+
+    def __init__(self):
+        self.plane_key = None
+        self.coef_key = None
+        self.bias_key = None
+        self.layer = None
+
+
+def _tensor_key(t: torch.Tensor):
+    return (t.data_ptr(), t._version, t.dtype, t.device, tuple(t.shape))
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f'bqq_b200: {what} lives on {t.device}; the BinaryQuadratic forward of this package '
+            'runs only on an sm_100 GPU (move the module with .cuda()); there is no CPU fallback')
+
+
+class _BqqForwardMixin:
+    """Shared engine of BinaryQuadratic and PackedBinaryQuadratic."""
+
+    # -- packed state -------------------------------------------------------
+    def _state(self) -> _PackedState:
+        st = self.__dict__.get('_bqq_state')
+        if st is None:
+            st = _PackedState()
+            self.__dict__['_bqq_state'] = st
+        return st
+
+    def __getstate__(self):
+        state = self.__dict__.copy()
+        state.pop('_bqq_state', None)      # derived GPU state never enters a pickle
+        return state
+
+    def _dims(self):
+        return _cabi.dims(self.bit_width, self.row_width, self.col_width, self.y_row, self.z_col,
+                          self.inter_dimension)
+
+    def _build_planes(self, st: _PackedState, device) -> None:
+        raise NotImplementedError
+
+    def _ensure_packed(self) -> _PackedState:
+        st = self._state()
+        src_y, src_z = self._plane_sources()
+        _require_cuda(src_y, 'the binary factor buffer')
+        device = src_y.device
+        pkey = (_tensor_key(src_y), _tensor_key(src_z))
+        if st.plane_key != pkey:
+            with torch.cuda.device(device):
+                if not lib.bqq_device_supported():
+                    raise RuntimeError('bqq_b200: the current GPU is not an sm_100 device')
+                st.dims = self._dims()
+                st.zplanes = torch.empty(lib.bqq_zplane_words(st.dims), dtype=torch.int32, device=device)
+                st.yplanes = torch.empty(lib.bqq_yplane_words(st.dims), dtype=torch.int32, device=device)
+                self._build_planes(st, device)
+            st.plane_key = pkey
+            st.coef_key = None
+            st.layer = None
+        ckey = tuple(_tensor_key(getattr(self, n)) for n in 'abcd')
+        if st.coef_key != ckey:
+            dt = self.a.dtype
+            if dt not in _DTYPE_CODE or any(getattr(self, n).dtype != dt for n in 'bcd'):
+                raise RuntimeError(f'bqq_b200: coefficients must share one of fp32/bf16/fp16, got {dt}')
+            with torch.cuda.device(device):
+                st.coef = torch.empty(lib.bqq_coeff_floats(st.dims), dtype=torch.float32, device=device)
+                a, b, c, d = (getattr(self, n).detach().contiguous() for n in 'abcd')
+                for t in (a, b, c, d):
+                    _require_cuda(t, 'a coefficient tensor')
+                check(lib.bqq_pack_coeffs(a.data_ptr(), b.data_ptr(), c.data_ptr(), d.data_ptr(),
+                                          _DTYPE_CODE[dt], st.dims, st.coef.data_ptr(),
+                                          torch.cuda.current_stream(device).cuda_stream), 'bqq_pack_coeffs')
+            st.coef_key = ckey
+            st.layer = None
+        bias = getattr(self, 'bias', None)
+        bkey = _tensor_key(bias) if bias is not None else None
+        if st.layer is None or st.bias_key != bkey:
+            if bias is not None:
+                _require_cuda(bias, 'the bias')
+                if bias.dtype not in _DTYPE_CODE:
+                    raise RuntimeError(f'bqq_b200: unsupported bias dtype {bias.dtype}')
+            st.layer = BqqLayer(st.dims, st.zplanes.data_ptr(), st.yplanes.data_ptr(), st.coef.data_ptr(),
+                                bias.data_ptr() if bias is not None else None,
+                                _DTYPE_CODE[bias.dtype] if bias is not None else 0, 0)
+            st.bias_key = bkey
+        return st
+
+    # -- forward ------------------------------------------------------------
+    def _check_inference_only(self, X) -> None:
+        if torch.is_grad_enabled():
+            needs = X.requires_grad or any(
+                p is not None and p.requires_grad
+                for p in (self.a, self.b, self.c, self.d, getattr(self, 'bias', None)))
+            if needs:
+                raise RuntimeError(
+                    'bqq_b200: this BinaryQuadratic forward is inference-only and records no autograd '
+                    'graph; call it under torch.no_grad() (training workflows need the reference module)')
+
+    def forward(self, X):
+        self._check_inference_only(X)
+        if X.dtype not in _DTYPE_CODE:
+            raise RuntimeError(f'bqq_b200: unsupported activation dtype {X.dtype} (fp32, bf16, fp16 only)')
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        in_f = self.col_width * self.z_col
+        out_f = self.row_width * self.y_row
+        if X.shape[-1] != in_f:
+            raise RuntimeError(f'bqq_b200: last dim of X is {X.shape[-1]}, layer expects {in_f}')
+        X = X.to(device)
+        x2 = X.reshape(-1, in_f)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        y = torch.empty((M, out_f), dtype=X.dtype, device=device)
+        if M == 0:
+            return y.reshape(*X.shape[:-1], out_f)
+        code = _DTYPE_CODE[X.dtype]
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            # up to 16 rows: bit-streaming decode kernel; more: tensor-core prefill path
+            if M <= _cabi.DECODE_MAX_M:
+                nbytes = lib.bqq_decode_workspace_bytes(st.dims, M)
+                ws = _workspace(device, 'decode', nbytes)
+                check(lib.bqq_forward_decode(st.layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(), code,
+                                             y.stride(0), ws.data_ptr(), ws.numel(), stream),
+                      'bqq_forward_decode')
+            else:
+                nbytes = lib.bqq_prefill_workspace_bytes(st.dims, M)
+                ws = _workspace(device, 'prefill', nbytes)
+                check(lib.bqq_forward_prefill(st.layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(),
+                                              code, y.stride(0), ws.data_ptr(), ws.numel(), stream),
+                      'bqq_forward_prefill')
+        return y.reshape(*X.shape[:-1], out_f)
+
+    def _weight_gpu(self, dtype):
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        out_f = self.row_width * self.y_row
+        in_f = self.col_width * self.z_col
+        W = torch.empty((out_f, in_f), dtype=dtype, device=device)
+        with torch.cuda.device(device):
+            check(lib.bqq_reconstruct_weight(st.layer, W.data_ptr(), _DTYPE_CODE[dtype], 1.0,
+                                             torch.cuda.current_stream(device).cuda_stream),
+                  'bqq_reconstruct_weight')
+        return W
+
+
+# ---------------------------------------------------------------------------
+# BinaryQuadratic
+# ---------------------------------------------------------------------------
+
+class BinaryQuadratic(_BqqForwardMixin, nn.Module):
+    """BQQ layer with {0,1} factors.  Constructor, buffers (`Y`, `Z` bool),
+    parameters (`a`, `b`, `c` [bw,rw,cw,1,1], `d` [rw,cw,1,1], `bias`) and the
+    attributes bit_width/row_width/col_width/y_row/inter_dimension/z_col match
+    the reference class (src/bqq_modules.py:18-32)."""
+
+    def __init__(self, Y, Z, A, bias=None):
+        super().__init__()
+        self.bit_width, self.row_width, self.col_width, self.y_row, self.inter_dimension = Y.shape
+        self.z_col = Z.shape[-1]
+        self.register_buffer('Y', Y > 0.5)
+        self.register_buffer('Z', Z > 0.5)
+        coef = [A[..., n].unsqueeze(-1).unsqueeze(-1) for n in range(4)]
+        self.a = nn.Parameter(coef[0].clone())
+        self.b = nn.Parameter(coef[1].clone())
+        self.c = nn.Parameter(coef[2].clone())
+        self.d = nn.Parameter(coef[3].sum(dim=0))       # one offset per patch: summed over bit layers
+        self.bias = nn.Parameter(bias) if bias is not None else None
+
+    def _plane_sources(self):
+        return self.Y, self.Z
+
+    def _build_planes(self, st, device):
+        Y = self.Y.contiguous()
+        Z = self.Z.contiguous()
+        if Y.dtype != torch.bool or Z.dtype != torch.bool:
+            Y, Z = Y > 0.5, Z > 0.5
+        n = self.bit_width * self.row_width * self.col_width
+        st.ysum = torch.empty(n * self.y_row, dtype=torch.uint8, device=device)
+        st.zsum = torch.empty(n * self.z_col, dtype=torch.uint8, device=device)
+        check(lib.bqq_pack_planes(Y.data_ptr(), Z.data_ptr(), st.dims, st.zplanes.data_ptr(),
+                                  st.yplanes.data_ptr(), st.ysum.data_ptr(), st.zsum.data_ptr(),
+                                  torch.cuda.current_stream(device).cuda_stream), 'bqq_pack_planes')
+
+    def get_weight(self, dtype=torch.float32):
+        """Dense W [out, in] (src/bqq_modules.py:48-55).  On the GPU it comes from
+        the popcount reconstruction kernel; before the module is moved to a GPU
+        it is evaluated with torch ops (not a forward path)."""
+        if self.Y.is_cuda and dtype in _DTYPE_CODE:
+            return self._weight_gpu(dtype)
+        Yf, Zf = self.Y.to(dtype), self.Z.to(dtype)
+        core = Yf @ Zf
+        W = (self.a.to(dtype) * core + self.b.to(dtype) * Yf.sum(-1, keepdim=True)
+             + self.c.to(dtype) * Zf.sum(-2, keepdim=True)).sum(0) + self.d.to(dtype)
+        return W.permute(0, 2, 1, 3).reshape(self.row_width * self.y_row, self.col_width * self.z_col)
+
+    def unpack_planes(self):
+        """Bit planes back to bool Y, Z (bit-exact round-trip check)."""
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        Y = torch.empty(self.Y.shape, dtype=torch.uint8, device=device)
+        Z = torch.empty(self.Z.shape, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            check(lib.bqq_unpack_planes(st.zplanes.data_ptr(), st.yplanes.data_ptr(), st.dims, Y.data_ptr(),
+                                        Z.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+                  'bqq_unpack_planes')
+        return Y.bool(), Z.bool()
+
+
+# ---------------------------------------------------------------------------
+# PackedBinaryQuadratic: the reference's uint8-packed checkpoints
+# ---------------------------------------------------------------------------
+
+class PackedBinaryQuadratic(_BqqForwardMixin, nn.Module):
+    """Accepts the reference's packed layer (src/bqq_modules.py:62-97): buffers
+    Y_packed [bw,rw,cw,P,ceil(r/8)], Z_packed [bw,rw,cw,Q,ceil(r/8)] (big-endian
+    uint8, Z transposed), Y_sum_i16, Z_sum_i16 and the same parameters.  The
+    bytes are re-packed on the GPU into this library's 32-bit planes at first
+    use; forward then runs the same kernels as BinaryQuadratic."""
+
+    def __init__(self, Y_packed, Z_packed, a, b, c, d, Y_sum_i16, Z_sum_i16,
+                 inter_dimension, y_row, z_col, bias=None):
+        super().__init__()
+        self.bit_width, self.row_width, self.col_width = Y_packed.shape[:3]
+        self.y_row, self.z_col, self.inter_dimension = y_row, z_col, inter_dimension
+        self._k8 = Y_packed.shape[-1]
+        self.register_buffer('Y_packed', Y_packed)
+        self.register_buffer('Z_packed', Z_packed)
+        self.register_buffer('Y_sum_i16', Y_sum_i16)
+        self.register_buffer('Z_sum_i16', Z_sum_i16)
+        self.a, self.b = nn.Parameter(a), nn.Parameter(b)
+        self.c, self.d = nn.Parameter(c), nn.Parameter(d)
+        self.bias = nn.Parameter(bias) if bias is not None else None
+
+    @classmethod
+    def from_unpacked(cls, bq: BinaryQuadratic) -> 'PackedBinaryQuadratic':
+        """BinaryQuadratic -> packed layer with the reference's byte layout
+        (src/bqq_modules.py:115-148): element 0 of the rank axis is the MSB."""
+        Y, Z = bq.Y, bq.Z
+        r = Y.shape[-1]
+        k8 = (r + 7) // 8
+        weights = (2 ** torch.arange(7, -1, -1, device=Y.device)).to(torch.int32)
+
+        def pack_last(bits):
+            pad = k8 * 8 - bits.shape[-1]
+            if pad:
+                bits = torch.nn.functional.pad(bits, (0, pad))
+            grouped = bits.reshape(*bits.shape[:-1], k8, 8).to(torch.int32)
+            return (grouped * weights).sum(-1).to(torch.uint8)
+
+        return cls(pack_last(Y), pack_last(Z.transpose(-1, -2)),
+                   bq.a.data.clone(), bq.b.data.clone(), bq.c.data.clone(), bq.d.data.clone(),
+                   Y.sum(-1, keepdim=True).to(torch.int16), Z.sum(-2, keepdim=True).to(torch.int16),
+                   r, Y.shape[-2], Z.shape[-1],
+                   bias=bq.bias.data.clone() if bq.bias is not None else None)
+
+    def _plane_sources(self):
+        return self.Y_packed, self.Z_packed
+
+    def _build_planes(self, st, device):
+        st.ysum = st.zsum = None
+        check(lib.bqq_repack_u8_planes(self.Y_packed.contiguous().data_ptr(),
+                                       self.Z_packed.contiguous().data_ptr(), st.dims,
+                                       st.zplanes.data_ptr(), st.yplanes.data_ptr(),
+                                       torch.cuda.current_stream(device).cuda_stream), 'bqq_repack_u8_planes')
+
+    def get_weight(self, dtype=torch.float32):
+        if not self.Y_packed.is_cuda or dtype not in _DTYPE_CODE:
+            raise RuntimeError('bqq_b200: PackedBinaryQuadratic.get_weight needs the module on an sm_100 GPU '
+                               'and an fp32/bf16/fp16 dtype')
+        return self._weight_gpu(dtype)
+
+
+def pack_binaryquadratic_model(model: nn.Module) -> nn.Module:
+    """Replace every BinaryQuadratic by its packed twin (src/bqq_modules.py:435-442)."""
+    for name, module in list(model.named_children()):
+        if isinstance(module, BinaryQuadratic):
+            setattr(model, name, PackedBinaryQuadratic.from_unpacked(module))
+        else:
+            pack_binaryquadratic_model(module)
+    return model
+
+
+# ---------------------------------------------------------------------------
+# patch list -> tensors, Linear -> BinaryQuadratic replacement
+# ---------------------------------------------------------------------------
+
+def get_matrices(patch_list, bit_width):
+    """Patch dicts {patch_row, patch_col, coeff, mat1, mat2, bit_idx} to dense
+    A [bw,rw,cw,4], Y [bw,rw,cw,P,r], Z [bw,rw,cw,r,Q]; entries whose bit_idx is
+    >= bit_width are skipped and patch geometry is taken from the first entry,
+    as in the reference (src/bqq_modules.py:485-507)."""
+    rw = max(int(p['patch_row']) for p in patch_list) + 1
+    cw = max(int(p['patch_col']) for p in patch_list) + 1
+    first = patch_list[0]
+    P, r = first['mat1'].shape
+    Q = first['mat2'].shape[1]
+    A = torch.zeros((bit_width, rw, cw, 4), dtype=first['coeff'].dtype)
+    Y = torch.zeros((bit_width, rw, cw, P, r), dtype=first['mat1'].dtype)
+    Z = torch.zeros((bit_width, rw, cw, r, Q), dtype=first['mat1'].dtype)
+    for p in patch_list:
+        k = int(p['bit_idx'])
+        if k >= bit_width:
+            continue
+        i, j = int(p['patch_row']), int(p['patch_col'])
+        A[k, i, j] = p['coeff']
+        Y[k, i, j] = p['mat1']
+        Z[k, i, j] = p['mat2']
+    return A, Y, Z
+
+
+def replace_linear_with_bqq(model: nn.Module, load_patches, bit_width: int, prefix: str = '') -> nn.Module:
+    """Walk the module tree and replace nn.Linear by BinaryQuadratic, skipping
+    any name that contains 'head', as lm/build_bqq_model.py:79-112 does.
+    `load_patches(weight_key)` returns the patch list of `<name>.weight` or None
+    (the reference reads it from its consolidated patch files)."""
+    for name, module in list(model.named_children()):
+        full = f'{prefix}.{name}' if prefix else name
+        if 'head' in full:
+            continue
+        if isinstance(module, nn.Linear):
+            patches = load_patches(f'{full}.weight')
+            if not patches:
+                continue
+            A, Y, Z = get_matrices(patches, bit_width)
+            setattr(model, name, BinaryQuadratic(Y, Z, A, bias=module.bias))
+        else:
+            replace_linear_with_bqq(module, load_patches, bit_width, prefix=full)
+    return model
+
+
+def shard_rows(bq: BinaryQuadratic, rank: int, world: int) -> BinaryQuadratic:
+    """Column-parallel shard: rank `rank` of `world` keeps the output-row patches
+    i in [rank*rw/world, (rank+1)*rw/world).  Row patches never interact, so the
+    concatenation of the shard outputs equals the unsharded output exactly."""
+    rw = bq.row_width
+    if rw % world != 0:
+        raise ValueError(f'row_width {rw} is not divisible by world size {world}')
+    per = rw // world
+    lo, hi = rank * per, (rank + 1) * per
+    out = BinaryQuadratic.__new__(BinaryQuadratic)
+    nn.Module.__init__(out)
+    out.bit_width, out.row_width, out.col_width = bq.bit_width, per, bq.col_width
+    out.y_row, out.inter_dimension, out.z_col = bq.y_row, bq.inter_dimension, bq.z_col
+    out.register_buffer('Y', bq.Y[:, lo:hi].contiguous())
+    out.register_buffer('Z', bq.Z[:, lo:hi].contiguous())
+    out.a = nn.Parameter(bq.a.data[:, lo:hi].contiguous())
+    out.b = nn.Parameter(bq.b.data[:, lo:hi].contiguous())
+    out.c = nn.Parameter(bq.c.data[:, lo:hi].contiguous())
+    out.d = nn.Parameter(bq.d.data[lo:hi].contiguous())
+    out.bias = (nn.Parameter(bq.bias.data[lo * bq.y_row:hi * bq.y_row].contiguous())
+                if bq.bias is not None else None)
+    return out

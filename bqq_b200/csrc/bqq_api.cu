@@ -1,0 +1,109 @@
+// C ABI of the library: argument checks and dispatch (see include/bqq_b200.h).
+#include "bqq_common.cuh"
+
+using namespace bqq;
+
+static int check_layer(const BqqLayer* L) {
+  if (!L) return BQQ_ERR_NULL;
+  int rc = check_dims(&L->dims);
+  if (rc) return rc;
+  if (!L->zplanes || !L->yplanes || !L->coef) return BQQ_ERR_NULL;
+  if (((uintptr_t)L->zplanes & 15) || ((uintptr_t)L->yplanes & 15) || ((uintptr_t)L->coef & 15))
+    return BQQ_ERR_MISALIGNED;
+  if (L->bias && !dtype_size(L->bias_dtype)) return BQQ_ERR_DTYPE;
+  return BQQ_OK;
+}
+
+static int check_io(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                    int64_t ldy) {
+  if (!x || !y) return BQQ_ERR_NULL;
+  if (!dtype_size(x_dtype) || !dtype_size(y_dtype)) return BQQ_ERR_DTYPE;
+  if (M <= 0) return BQQ_ERR_BAD_SHAPE;
+  Geom g(L->dims);
+  if (ldx < g.in_features() || ldy < g.out_features()) return BQQ_ERR_BAD_SHAPE;
+  if (((uintptr_t)x % dtype_size(x_dtype)) || ((uintptr_t)y % dtype_size(y_dtype))) return BQQ_ERR_MISALIGNED;
+  return BQQ_OK;
+}
+
+extern "C" {
+
+int bqq_abi_version(void) { return BQQ_ABI_VERSION; }
+
+const char* bqq_strerror(int rc) {
+  switch (rc) {
+    case BQQ_OK: return "ok";
+    case BQQ_ERR_NULL: return "a required pointer is NULL";
+    case BQQ_ERR_BAD_SHAPE: return "a dimension is non-positive or inconsistent";
+    case BQQ_ERR_UNSUPPORTED: return "patch geometry or batch size outside the kernel limits";
+    case BQQ_ERR_MISALIGNED: return "a pointer or leading dimension is misaligned";
+    case BQQ_ERR_WORKSPACE: return "workspace missing or too small";
+    case BQQ_ERR_DTYPE: return "unknown element type code";
+    case BQQ_ERR_CUDA: return "a CUDA call failed";
+    case BQQ_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+    case BQQ_ERR_NO_DEVICE: return "no sm_100 GPU is current";
+    default: return "unknown bqq error code";
+  }
+}
+
+int bqq_device_supported(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return major == 10 ? 1 : 0;
+}
+
+size_t bqq_decode_workspace_bytes(const BqqDims* dims, int M) {
+  if (check_dims(dims) != BQQ_OK || M <= 0) return 0;
+  return decode_workspace_bytes(dims, M > BQQ_DECODE_MAX_M ? BQQ_DECODE_MAX_M : M);
+}
+
+int bqq_forward_decode(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
+                       int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  rc = check_io(layer, x, x_dtype, M, ldx, y, y_dtype, ldy);
+  if (rc) return rc;
+  if (M > BQQ_DECODE_MAX_M) return BQQ_ERR_UNSUPPORTED;
+  return decode_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
+                       (cudaStream_t)stream);
+}
+
+size_t bqq_prefill_workspace_bytes(const BqqDims* dims, int M) {
+  if (check_dims(dims) != BQQ_OK || M <= 0) return 0;
+  return prefill_workspace_bytes(dims, M);
+}
+
+int bqq_forward_prefill(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
+                        int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  rc = check_io(layer, x, x_dtype, M, ldx, y, y_dtype, ldy);
+  if (rc) return rc;
+  return prefill_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
+                        (cudaStream_t)stream);
+}
+
+size_t bqq_forward_workspace_bytes(const BqqDims* dims, int M) {
+  return M <= BQQ_DECODE_MAX_M ? bqq_decode_workspace_bytes(dims, M) : bqq_prefill_workspace_bytes(dims, M);
+}
+
+int bqq_forward(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
+  if (M <= BQQ_DECODE_MAX_M)
+    return bqq_forward_decode(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
+  return bqq_forward_prefill(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
+}
+
+int bqq_reconstruct_weight(const BqqLayer* layer, void* W, int w_dtype, float scale, void* stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  if (!W) return BQQ_ERR_NULL;
+  if (!dtype_size(w_dtype)) return BQQ_ERR_DTYPE;
+  return reconstruct_launch(layer, W, w_dtype, scale, (cudaStream_t)stream);
+}
+
+}  // extern "C"

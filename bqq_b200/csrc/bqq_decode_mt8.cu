@@ -1,0 +1,5 @@
+// Decode kernel instantiations for a batch tile of 8 row(s) of X.
+#include "bqq_decode_kernel.cuh"
+namespace bqq {
+template int decode_launch_mt<8>(const DecodeParams&, const DecodePlan&, int, int, cudaStream_t);
+}

@@ -1,0 +1,383 @@
+// Prefill forward: y[M,N] = x[M,K] @ W[N,K]^T with W rebuilt once from the packed
+// planes into scratch memory (fp16, scaled by a power of two so that the bound
+// on |W| maps to 2^14), then a TMA + tcgen05 tensor-core GEMM with the fp32
+// accumulator in tensor memory.  Replaces reconstruct_W_kernel + torch::mm of
+// the reference (neural_network_compression/src/bqq_cuda.cu:198-246, 367-383).
+//
+// GEMM kernel, one 128 x BN output tile per CTA, 6 warps:
+//   warp 0   TMA producer: 4-stage ring of {A 128x64, B BNx64} 16-bit tiles,
+//            128-byte swizzle, completion on mbarriers
+//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN,
+//            K=16 per instruction) and commits stage releases to mbarriers
+//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, scale, bias, convert, store
+// Every mbarrier wait is bounded by a clock budget; on expiry the kernel records
+// a status code in global memory, drains its copies and returns.
+#include <cuda.h>
+
+#include "bqq_common.cuh"
+
+namespace bqq {
+
+int reconstruct_launch_dev(const BqqLayer* L, void* W, int w_dtype, float scale, const float* trailer,
+                           cudaStream_t st);
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;          // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr long long kWaitBudget = 4000000000LL;   // clock cycles (~2 s) before a wait gives up
+
+// ---- PTX wrappers -----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the clock budget ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitBudget) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
+// 128-byte swizzled, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, 16-byte units
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                              // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                              // 128-byte swizzle
+  return d;
+}
+
+struct GemmParams {
+  void* y;
+  const void* bias;
+  const float* trailer;      // coefficient trailer (bound on |W|)
+  float bound_mult;          // bw * r
+  unsigned* status;          // device word, set nonzero when a wait timed out
+  int64_t ldy;
+  int y_dtype, bias_dtype;
+  int M, N, K;
+  int a_passes;              // 1, or 2 when x was split into hi + lo halves
+  uint32_t idesc;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
+                const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t gsm[];
+  constexpr uint32_t kABytes = kBM * kBK * 2;
+  constexpr uint32_t kBBytes = BN * kBK * 2;
+  // 1024-byte aligned tiles (required by the 128-byte swizzle)
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gsm) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = base;
+  uint8_t* sB = base + kStages * kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + kStages * kBBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* acc_bar = empty_bar + kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  volatile uint32_t* failed = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * kBM;
+  const int kblocks = (p.K + kBK - 1) / kBK;
+  const int iters = kblocks * p.a_passes;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+    mbar_init(acc_bar, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int it = 0; it < iters; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+        if (*failed || !mbar_wait(empty_bar + s, ph ^ 1u)) { *failed = 1; break; }
+        mbar_expect_tx(full_bar + s, kABytes + kBBytes);
+        const int kb = it % kblocks;
+        const CUtensorMap* ma = (it < kblocks) ? &map_a0 : &map_a1;
+        tma_load_2d(sA + s * kABytes, ma, full_bar + s, kb * kBK, m0);
+        tma_load_2d(sB + s * kBBytes, &map_b, full_bar + s, kb * kBK, n0);
+        issued = it + 1;
+      }
+      if (*failed) {
+        // drain: copies already issued must land before the CTA exits
+        int first = issued > kStages ? issued - kStages : 0;
+        for (int it = first; it < issued; ++it)
+          mbar_wait(full_bar + it % kStages, (uint32_t)(it / kStages) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1u;
+        if (*failed || !mbar_wait(full_bar + s, ph)) { *failed = 1; ok = false; break; }
+        tc_fence_after();
+        const uint64_t adesc = make_smem_desc(smem_u32(sA + s * kABytes));
+        const uint64_t bdesc = make_smem_desc(smem_u32(sB + s * kBBytes));
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units per step
+          tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc, (it | k) != 0 ? 1u : 0u);
+        tc_commit(empty_bar + s);            // frees the stage when these MMAs have read it
+      }
+      tc_commit(acc_bar);                    // accumulator complete (or abandoned)
+    }
+  } else {
+    // epilogue warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31
+    const int quarter = warp & 3;
+    const bool ok = mbar_wait(acc_bar, 0) && !*failed;
+    if (!ok) *failed = 1;
+    tc_fence_after();
+    if (ok) {
+      const float inv_scale = 1.f / w_scale_from_trailer(p.trailer, p.bound_mult);
+      const int m = m0 + quarter * 32 + lane;
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+        tc_wait_ld();
+        const int nb = n0 + c * 32;
+        if (m < p.M && nb < p.N) {
+          const size_t row = (size_t)m * p.ldy;
+          const bool full = nb + 32 <= p.N;
+          if (full && p.y_dtype != BQQ_F32 && (((row + nb) * 2 + (uintptr_t)p.y) & 15) == 0) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.y) + row + nb);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float f0 = __uint_as_float(v[g * 8 + 2 * e]) * inv_scale;
+                float f1 = __uint_as_float(v[g * 8 + 2 * e + 1]) * inv_scale;
+                if (p.bias) {
+                  f0 += load_as_float(p.bias, nb + g * 8 + 2 * e, p.bias_dtype);
+                  f1 += load_as_float(p.bias, nb + g * 8 + 2 * e + 1, p.bias_dtype);
+                }
+                if (p.y_dtype == BQQ_BF16) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                  w[e] = *reinterpret_cast<uint32_t*>(&h);
+                } else {
+                  __half2 h = __floats2half2_rn(f0, f1);
+                  w[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              }
+              dst[g] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (nb + e < p.N) {
+                float f = __uint_as_float(v[e]) * inv_scale;
+                if (p.bias) f += load_as_float(p.bias, nb + e, p.bias_dtype);
+                store_from_float(p.y, row + nb + e, p.y_dtype, f);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *failed) atomicExch(p.status, 1u);
+}
+
+// ---- x staging: any dtype / stride -> dense 16-bit rows (hi, lo for fp32) ----
+__global__ void stage_x_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int K, int Kp,
+                               uint16_t* __restrict__ hi, uint16_t* __restrict__ lo) {
+  const size_t n = (size_t)M * Kp;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < n; t += (size_t)gridDim.x * blockDim.x) {
+    const int k = (int)(t % Kp);
+    const size_t m = t / Kp;
+    if (x_dtype == BQQ_F32) {
+      float v = k < K ? reinterpret_cast<const float*>(x)[m * ldx + k] : 0.f;
+      __nv_bfloat16 h = __float2bfloat16_rn(v);
+      __nv_bfloat16 l = __float2bfloat16_rn(v - __bfloat162float(h));
+      hi[t] = *reinterpret_cast<uint16_t*>(&h);
+      lo[t] = *reinterpret_cast<uint16_t*>(&l);
+    } else {
+      hi[t] = k < K ? reinterpret_cast<const uint16_t*>(x)[m * ldx + k] : (uint16_t)0;
+    }
+  }
+}
+
+// ---- host side -----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D row-major [rows][cols] 16-bit tensor, box = box_rows x 64 columns, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, bool bf16, uint64_t rows, uint64_t cols,
+                    uint64_t ld_elems, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return BQQ_ERR_CUDA;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld_elems * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? BQQ_OK : BQQ_ERR_CUDA;
+}
+
+static inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+// workspace: [status 256 B][W fp16 N x K][x hi M x K][x lo M x K]
+size_t prefill_workspace_bytes(const BqqDims* dims, int M) {
+  Geom g(*dims);
+  const size_t K = g.in_features();
+  return 256 + up256((size_t)g.out_features() * K * 2) + 2 * up256((size_t)M * K * 2);
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
+                       cudaStream_t st) {
+  const size_t smem = 1024 + (size_t)kStages * (kBM * kBK * 2 + BN * kBK * 2) + 256;
+  auto kern = bqq_gemm_kernel<BN>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return BQQ_ERR_CUDA;
+  dim3 grid((p.N + BN - 1) / BN, (p.M + kBM - 1) / kBM);
+  kern<<<grid, kGemmThreads, smem, st>>>(a0, a1, b, p);
+  return launch_status();
+}
+
+int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                   int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t st) {
+  Geom g(L->dims);
+  const int N = g.out_features(), K = g.in_features();
+  if (K % 8 != 0) return BQQ_ERR_UNSUPPORTED;   // 16-byte row pitch for the TMA descriptors
+  if (!ws || ws_bytes < prefill_workspace_bytes(&L->dims, M)) return BQQ_ERR_WORKSPACE;
+  if (((uintptr_t)ws & 255) != 0) return BQQ_ERR_MISALIGNED;
+  uint8_t* wsb = reinterpret_cast<uint8_t*>(ws);
+  unsigned* status = reinterpret_cast<unsigned*>(wsb);
+  uint16_t* W = reinterpret_cast<uint16_t*>(wsb + 256);
+  uint16_t* xhi = reinterpret_cast<uint16_t*>(wsb + 256 + up256((size_t)N * K * 2));
+  uint16_t* xlo = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(xhi) + up256((size_t)M * K * 2));
+  const float* trailer = L->coef + g.coef_records() * 4;   // written by bqq_pack_coeffs
+
+  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return BQQ_ERR_CUDA;
+
+  // 1. dense W (fp16, scaled by the power of two derived from the bound) into scratch
+  int rc = reconstruct_launch_dev(L, W, BQQ_F16, 1.f, trailer, st);
+  if (rc) return rc;
+
+  // 2. x: used in place when it is a 16-bit tensor with TMA-compatible pitch, else staged
+  const bool direct = x_dtype != BQQ_F32 && (ldx % 8) == 0 && ((uintptr_t)x & 15) == 0;
+  const void* a_ptr = x;
+  int64_t a_ld = ldx;
+  int passes = 1;
+  if (!direct) {
+    size_t n = (size_t)M * K;
+    int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    stage_x_kernel<<<blocks, 256, 0, st>>>(x, x_dtype, ldx, M, K, K, xhi, xlo);
+    rc = launch_status();
+    if (rc) return rc;
+    a_ptr = xhi;
+    a_ld = K;
+    passes = x_dtype == BQQ_F32 ? 2 : 1;
+  }
+  const bool a_bf16 = x_dtype != BQQ_F16;   // fp32 input is staged as bf16 hi + lo
+
+  const int BN = (N >= 256) ? 256 : 128;
+  CUtensorMap ma0, ma1, mb;
+  rc = make_map(&ma0, a_ptr, a_bf16, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, kBM);
+  if (rc) return rc;
+  rc = make_map(&ma1, passes == 2 ? (const void*)xlo : a_ptr, a_bf16, (uint64_t)M, (uint64_t)K,
+                passes == 2 ? (uint64_t)K : (uint64_t)a_ld, kBM);
+  if (rc) return rc;
+  rc = make_map(&mb, W, false, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BN);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.y = y; p.bias = L->bias; p.trailer = trailer; p.bound_mult = (float)(g.bw * g.r); p.status = status;
+  p.ldy = ldy; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
+  p.M = M; p.N = N; p.K = K; p.a_passes = passes;
+  // instruction descriptor: fp32 accumulate, A format, B = fp16, both K-major, N and M extents
+  p.idesc = (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | (0u << 10) | ((uint32_t)(BN >> 3) << 17) |
+            ((uint32_t)(kBM >> 4) << 24);
+  return BN == 256 ? launch_gemm<256>(ma0, ma1, mb, p, st) : launch_gemm<128>(ma0, ma1, mb, p, st);
+}
+
+}  // namespace bqq

@@ -1,0 +1,180 @@
+"""GPU parity: the CUDA forward through the module / C ABI against the oracle and the
+golden outputs of the reference.  Tolerance: max|y - y_ref| / max|y_ref| <= 1e-3 with
+y_ref the reference forward evaluated in fp32 on the same (already rounded) inputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bqq_oracle as O
+from tests.helpers import LAYER_CASES, load_golden, oracle_forward_t, synth_layer
+from tests.test_gpu_pack import _module_from_golden
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3        # contract
+TOL_FP32 = 2e-5   # what fp32 activations through the fp32-accumulating decode kernel should reach
+
+
+def _run(bq, X):
+    with torch.no_grad():
+        y = bq(X)
+    torch.cuda.synchronize()
+    return y
+
+
+@pytest.mark.parametrize('name', LAYER_CASES)
+def test_golden_cases(name):
+    g = load_golden(name)
+    bq = _module_from_golden(g)
+    X = torch.from_numpy(g['X'])
+    if bool(g['x_is_bf16']):
+        X = X.to(torch.bfloat16)
+    y = _run(bq, X.cuda())
+    assert y.dtype == X.dtype and tuple(y.shape) == tuple(g['y_ref_fp32'].shape)
+    err = O.max_rel_err(y.float().cpu().numpy(), g['y_ref_fp32'])
+    # bf16 outputs carry their own rounding (2^-9 relative) on top of the compute error
+    assert err < (4e-3 if X.dtype == torch.bfloat16 else TOL_FP32), err
+    if X.dtype == torch.bfloat16:
+        y32 = _run(bq, X.float().cuda())
+        assert O.max_rel_err(y32.cpu().numpy(), g['y_ref_fp32']) < TOL_FP32
+
+
+def test_config1_golden():
+    g = load_golden('config1_4096')
+    Y, Z, A, _, X = synth_layer(2, 128, 128, 32, 32, 32, 1, seed=0)
+    assert np.array_equal(X.numpy(), g['X'])
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    y = _run(bq, X.cuda())
+    assert O.max_rel_err(y.cpu().numpy(), g['y_ref_fp64']) < TOL_FP32
+
+
+DECODE_SHAPES = [
+    # bw, rw, cw, P, Q, r
+    (2, 16, 24, 32, 32, 32), (3, 8, 8, 32, 32, 32), (4, 8, 4, 32, 32, 32),
+    (2, 8, 8, 64, 64, 32), (3, 4, 6, 64, 64, 64), (2, 2, 3, 128, 128, 64),
+    (2, 4, 4, 16, 16, 16), (2, 2, 2, 32, 32, 12), (1, 3, 5, 96, 40, 33), (5, 2, 3, 32, 64, 7),
+]
+
+
+@pytest.mark.parametrize('shape', DECODE_SHAPES)
+@pytest.mark.parametrize('M', [1, 2, 4, 5, 16])
+def test_decode_against_oracle(shape, M):
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(*shape, M, seed=sum(shape) + M, bias=(M % 2 == 0))
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    ref = oracle_forward_t(Y, Z, A, bias, X)
+    y = _run(bq, X.cuda())
+    assert O.max_rel_err(y.cpu().numpy(), ref) < TOL_FP32
+    Xb = X.to(torch.bfloat16)
+    refb = oracle_forward_t(Y, Z, A, bias, Xb)
+    yb = _run(bq, Xb.cuda())
+    assert yb.dtype == torch.bfloat16
+    # compare before the final bf16 rounding dominates: |err| <= 1e-3 of max plus bf16 output rounding
+    assert O.max_rel_err(yb.float().cpu().numpy(), refb) < TOL + 2 ** -8
+    yh = _run(bq, X.half().cuda())
+    assert O.max_rel_err(yh.float().cpu().numpy(), oracle_forward_t(Y, Z, A, bias, X.half())) < TOL + 2 ** -10
+
+
+@pytest.mark.parametrize('shape,M', [((2, 8, 8, 32, 32, 32), 64), ((2, 16, 8, 32, 32, 32), 200),
+                                     ((3, 4, 6, 64, 64, 64), 130), ((2, 3, 2, 64, 64, 32), 17),
+                                     ((2, 40, 16, 32, 32, 32), 300)])
+def test_prefill_against_oracle(shape, M):
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(*shape, M, seed=sum(shape) + M, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    for dt in (torch.bfloat16, torch.float16, torch.float32):
+        Xd = X.to(dt)
+        ref = oracle_forward_t(Y, Z, A, bias, Xd)
+        y = _run(bq, Xd.cuda())
+        assert y.dtype == dt
+        out_round = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -10, torch.float32: 0.0}[dt]
+        err = O.max_rel_err(y.float().cpu().numpy(), ref)
+        assert err < TOL + out_round, (dt, err)
+
+
+def test_prefill_fp32_output_tolerance():
+    """Config-3-like contraction (K = 4096) with fp32 outputs so only compute error remains."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, _, X = synth_layer(2, 8, 128, 32, 32, 32, 256, seed=5, x_dtype=torch.bfloat16)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    ref = oracle_forward_t(Y, Z, A, None, X)
+    st = bq._ensure_packed()
+    from bqq_b200 import _cabi
+    from bqq_b200.bqq_modules import _workspace
+    xg = X.cuda()
+    y = torch.empty(256, 256, dtype=torch.float32, device='cuda')
+    ws = _workspace(xg.device, 'prefill', _cabi.lib.bqq_prefill_workspace_bytes(st.dims, 256))
+    rc = _cabi.lib.bqq_forward_prefill(st.layer, xg.data_ptr(), _cabi.BF16, 256, xg.stride(0), y.data_ptr(),
+                                       _cabi.F32, y.stride(0), ws.data_ptr(), ws.numel(),
+                                       torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(ws[:4].view(torch.int32).item()) == 0          # no bounded wait gave up
+    assert O.max_rel_err(y.cpu().numpy(), ref) < TOL
+
+
+def test_leading_dims_and_strides():
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, _, _ = synth_layer(2, 4, 4, 32, 32, 32, 1, seed=3)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    X = torch.randn(2, 3, 128, generator=torch.Generator().manual_seed(1))
+    y = _run(bq, X.cuda())
+    assert tuple(y.shape) == (2, 3, 128)
+    ref = oracle_forward_t(Y, Z, A, None, X.reshape(6, 128)).reshape(2, 3, 128)
+    assert O.max_rel_err(y.cpu().numpy(), ref) < TOL_FP32
+    # X on the host is moved to the layer's device, as the reference does with X.to(device)
+    y2 = _run(bq, X)
+    assert y2.is_cuda and torch.equal(y2, y)
+    # row-strided view
+    big = torch.randn(6, 256, generator=torch.Generator().manual_seed(2)).cuda()
+    view = big[:, :128]
+    y3 = _run(bq, view)
+    ref3 = oracle_forward_t(Y, Z, A, None, view.cpu())
+    assert O.max_rel_err(y3.cpu().numpy(), ref3) < TOL_FP32
+    assert _run(bq, torch.empty(0, 128).cuda()).shape == (0, 128)
+
+
+def test_get_weight_gpu():
+    for name in ('layer_0', 'layer_2', 'extend_3bit', 'fused_s123'):
+        g = load_golden(name)
+        bq = _module_from_golden(g)
+        W = bq.get_weight(torch.float32).cpu().numpy()
+        Wref = O.dense_weight(g['Y'], g['Z'], g['a'], g['b'], g['c'], g['d'])
+        assert np.abs(W - Wref).max() <= 1e-5 * max(1.0, np.abs(Wref).max())
+        Wb = bq.get_weight(torch.bfloat16)
+        assert Wb.dtype == torch.bfloat16
+        assert np.abs(Wb.float().cpu().numpy() - Wref).max() <= 2 ** -8 * np.abs(Wref).max()
+
+
+def test_decode_is_deterministic_and_workspace_reusable():
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, _, X = synth_layer(2, 32, 64, 32, 32, 32, 4, seed=9)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    xg = X.cuda()
+    y0 = _run(bq, xg)
+    for _ in range(5):
+        assert torch.equal(_run(bq, xg), y0)
+
+
+def test_linearity_full_size():
+    """Size-independent property at a full configuration size (4096 x 14336, 2 bit layers):
+    f(x1 + x2) = f(x1) + f(x2) and f(0) = 0, plus parity of a random output subset rebuilt by the oracle."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, P, Q, r = 2, 128, 448, 32, 32, 32
+    gen = torch.Generator(device='cuda').manual_seed(4)
+    Y = torch.rand(bw, rw, cw, P, r, generator=gen, device='cuda') > 0.5
+    Z = torch.rand(bw, rw, cw, r, Q, generator=gen, device='cuda') > 0.5
+    A = torch.randn(bw, rw, cw, 4, generator=gen, device='cuda') * 0.02
+    bq = BinaryQuadratic(Y, Z, A)
+    x1 = torch.randn(1, cw * Q, generator=gen, device='cuda')
+    x2 = torch.randn(1, cw * Q, generator=gen, device='cuda')
+    y1, y2, y12 = _run(bq, x1), _run(bq, x2), _run(bq, x1 + x2)
+    scale = y12.abs().max().item()
+    assert (y12 - (y1 + y2)).abs().max().item() < 1e-4 * scale
+    assert _run(bq, torch.zeros_like(x1)).abs().max().item() == 0.0
+    # oracle on 3 row patches only (the rest of the layer does not influence them)
+    for i in (0, 57, 127):
+        a, b, c, d = O.split_coefficients(A[:, i:i + 1].cpu().numpy())
+        ref = O.forward(Y[:, i:i + 1].cpu().numpy(), Z[:, i:i + 1].cpu().numpy(), a, b, c, d, x1.cpu().numpy())
+        got = y1[:, i * P:(i + 1) * P].cpu().numpy()
+        assert np.abs(got - ref).max() < TOL_FP32 * scale

@@ -1,0 +1,119 @@
+"""GPU: drop-in behaviour of the module (pickles, construction without __init__,
+in-place parameter updates, dtype casts, error behaviour)."""
+import io
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import bqq_oracle as O
+from tests.helpers import oracle_forward_t, synth_layer
+
+pytestmark = pytest.mark.gpu
+
+
+def _fwd(m, X):
+    with torch.no_grad():
+        return m(X)
+
+
+def test_pickle_round_trip_and_install():
+    import bqq_b200
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bqq_b200.install()
+    Y, Z, A, bias, X = synth_layer(2, 4, 4, 32, 32, 32, 3, seed=1, bias=True)
+    model = nn.Sequential(BinaryQuadratic(Y.float(), Z.float(), A, bias=bias)).cuda()
+    y0 = _fwd(model, X.cuda())
+    buf = io.BytesIO()
+    torch.save(model, buf)                      # whole-module pickle, as the reference saves models
+    assert b'bqq_modules' in buf.getvalue() and b'_bqq_state' not in buf.getvalue()
+    buf.seek(0)
+    model2 = torch.load(buf, weights_only=False)
+    assert torch.equal(_fwd(model2, X.cuda()), y0)
+    # state_dict route
+    m3 = BinaryQuadratic(torch.zeros_like(Y).float(), torch.zeros_like(Z).float(), torch.zeros_like(A),
+                         bias=torch.zeros_like(bias)).cuda()
+    m3.load_state_dict(model[0].state_dict())
+    assert torch.equal(_fwd(m3, X.cuda()), y0)
+
+
+def test_construct_without_init():
+    """The reference benchmark builds layers with __new__ and fills attributes by hand."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, gs = 2, 4, 6, 32
+    g = torch.Generator().manual_seed(2)
+    Y = torch.randint(0, 2, (bw, rw, cw, gs, gs), generator=g).bool()
+    Z = torch.randint(0, 2, (bw, rw, cw, gs, gs), generator=g).bool()
+    A = torch.randn(bw, rw, cw, 4, generator=g) * 0.01
+    bq = BinaryQuadratic.__new__(BinaryQuadratic)
+    nn.Module.__init__(bq)
+    bq.bit_width, bq.row_width, bq.col_width = bw, rw, cw
+    bq.y_row, bq.inter_dimension, bq.z_col = gs, gs, gs
+    bq.register_buffer('Y', Y)
+    bq.register_buffer('Z', Z)
+    bq.a = nn.Parameter(A[..., 0].unsqueeze(-1).unsqueeze(-1))
+    bq.b = nn.Parameter(A[..., 1].unsqueeze(-1).unsqueeze(-1))
+    bq.c = nn.Parameter(A[..., 2].unsqueeze(-1).unsqueeze(-1))
+    bq.d = nn.Parameter(A[..., 3].unsqueeze(-1).unsqueeze(-1).sum(dim=0))
+    bq.bias = None
+    bq = bq.cuda()
+    X = torch.randn(1, cw * gs, generator=g)
+    assert O.max_rel_err(_fwd(bq, X.cuda()).cpu().numpy(), oracle_forward_t(Y, Z, A, None, X)) < 2e-5
+
+
+def test_in_place_coefficient_update_is_seen():
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, _, X = synth_layer(2, 4, 4, 32, 32, 32, 2, seed=3)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    y0 = _fwd(bq, X.cuda())
+    with torch.no_grad():
+        bq.a.data[...] = bq.a.data * 2.0        # scale refinement rewrites .data in place
+        bq.d.data.add_(0.5)
+    A2 = A.clone()
+    A2[..., 0] *= 2.0
+    A2[0, ..., 3] += 0.5
+    y1 = _fwd(bq, X.cuda())
+    assert not torch.equal(y0, y1)
+    assert O.max_rel_err(y1.cpu().numpy(), oracle_forward_t(Y, Z, A2, None, X)) < 2e-5
+
+
+def test_bfloat16_cast_and_device_moves():
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(2, 4, 4, 64, 64, 32, 4, seed=4, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias)
+    bq = bq.cuda().bfloat16()                   # model.bfloat16() casts the coefficient parameters
+    assert bq.a.dtype == torch.bfloat16 and bq.Y.dtype == torch.bool
+    Ab = A.to(torch.bfloat16).float()
+    Ab[0, ..., 3] = A[..., 3].sum(0).to(torch.bfloat16).float()
+    Ab[1:, ..., 3] = 0
+    Xb = X.to(torch.bfloat16)
+    ref = oracle_forward_t(Y, Z, Ab, bias.to(torch.bfloat16).float(), Xb)
+    y = _fwd(bq, Xb.cuda())
+    assert O.max_rel_err(y.float().cpu().numpy(), ref) < 1e-3 + 2 ** -8
+
+
+def test_errors():
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, _, X = synth_layer(1, 2, 2, 32, 32, 32, 1, seed=6)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    with pytest.raises(RuntimeError, match='inference-only'):
+        bq(X.cuda())
+    with torch.no_grad():
+        with pytest.raises(RuntimeError, match='last dim'):
+            bq(torch.randn(1, 65).cuda())
+        with pytest.raises(RuntimeError, match='unsupported activation dtype'):
+            bq(X.double().cuda())
+
+
+def test_sharded_rows_equal_unsharded():
+    """Column-parallel shards (output-row patches) reproduce the full layer (fp32 summation
+    order may differ with the number of row patches per launch, nothing else)."""
+    from bqq_b200.bqq_modules import BinaryQuadratic, shard_rows
+    Y, Z, A, bias, X = synth_layer(2, 8, 6, 32, 32, 32, 4, seed=8, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    full = _fwd(bq, X.cuda())
+    for world in (2, 4, 8):
+        parts = [_fwd(shard_rows(bq, r, world), X.cuda()) for r in range(world)]
+        got = torch.cat(parts, dim=-1)
+        assert (got - full).abs().max().item() <= 1e-5 * full.abs().max().item()
