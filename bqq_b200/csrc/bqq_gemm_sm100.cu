@@ -1,7 +1,10 @@
 // Prefill forward: y[M,N] = x[M,K] @ W[N,K]^T with W rebuilt once from the packed
-// planes into scratch memory (fp16, scaled by a power of two so that the bound
-// on |W| maps to 2^14), then a TMA + tcgen05 tensor-core GEMM with the fp32
-// accumulator in tensor memory.  Replaces reconstruct_W_kernel + torch::mm of
+// planes into scratch memory, then a TMA + tcgen05 tensor-core GEMM with the fp32
+// accumulator in tensor memory.  W is stored in the 16-bit format of the
+// activations: fp16 (scaled by a power of two so that the bound on |W| maps to
+// 2^14) for fp16 x, or as a bf16 pair hi + lo for bf16 x, in which case the K
+// loop runs once per (x part, W part) pass into the same accumulator; fp32 x is
+// split into bf16 hi + lo the same way (passes hi*hi, hi*lo, lo*hi).  Replaces reconstruct_W_kernel + torch::mm of
 // the reference (neural_network_compression/src/bqq_cuda.cu:198-246, 367-383).
 //
 // GEMM kernel, one 128 x BN output tile per CTA, 6 warps:
@@ -18,7 +21,7 @@
 
 namespace bqq {
 
-int reconstruct_launch_dev(const BqqLayer* L, void* W, int w_dtype, float scale, const float* trailer,
+int reconstruct_launch_dev(const BqqLayer* L, void* W, void* W_lo, int w_dtype, float scale, const float* trailer,
                            cudaStream_t st);
 
 constexpr int kBM = 128;
@@ -89,6 +92,7 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                              // leading byte offset (one 16-byte unit; unused by swizzled K-major)
   d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
   d |= (uint64_t)1 << 46;                              // descriptor version of this architecture
   d |= (uint64_t)2 << 61;                              // 128-byte swizzle
@@ -104,8 +108,11 @@ struct GemmParams {
   int64_t ldy;
   int y_dtype, bias_dtype;
   int M, N, K;
-  int a_passes;              // 1, or 2 when x was split into hi + lo halves
+  int passes;                // K sweeps accumulated into one tile (1..3)
+  int a_sel[3];              // per pass: 0 = first activation map, 1 = second (low half of fp32 x)
+  int b_row[3];              // per pass: row offset into the stacked W map (0 = hi / only part, N = lo part)
   uint32_t idesc;
+  volatile unsigned* dbg;    // optional host-mapped progress markers (NULL in normal use)
 };
 
 template <int BN>
@@ -130,7 +137,7 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
   const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * kBM;
   const int kblocks = (p.K + kBK - 1) / kBK;
-  const int iters = kblocks * p.a_passes;
+  const int iters = kblocks * p.passes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
@@ -146,6 +153,9 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool dbg_on = p.dbg && blockIdx.x == 0 && blockIdx.y == 0;
+#define BQQ_MARK(idx, val) do { if (dbg_on) { p.dbg[idx] = (val); __threadfence_system(); } } while (0)
+  if (threadIdx.x == 0) BQQ_MARK(1, tmem_base | 0x80000000u);   // setup + tensor-memory allocation done
 
   if (warp == 0) {
     if (lane == 0) {
@@ -156,9 +166,11 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
         if (*failed || !mbar_wait(empty_bar + s, ph ^ 1u)) { *failed = 1; break; }
         mbar_expect_tx(full_bar + s, kABytes + kBBytes);
         const int kb = it % kblocks;
-        const CUtensorMap* ma = (it < kblocks) ? &map_a0 : &map_a1;
+        const int pass = it / kblocks;
+        const CUtensorMap* ma = p.a_sel[pass] == 0 ? &map_a0 : &map_a1;
         tma_load_2d(sA + s * kABytes, ma, full_bar + s, kb * kBK, m0);
-        tma_load_2d(sB + s * kBBytes, &map_b, full_bar + s, kb * kBK, n0);
+        tma_load_2d(sB + s * kBBytes, &map_b, full_bar + s, kb * kBK, p.b_row[pass] + n0);
+        if (it == 0) BQQ_MARK(2, 1u);       // first copies issued
         issued = it + 1;
       }
       if (*failed) {
@@ -175,29 +187,35 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
         const int s = it % kStages;
         const uint32_t ph = (uint32_t)(it / kStages) & 1u;
         if (*failed || !mbar_wait(full_bar + s, ph)) { *failed = 1; ok = false; break; }
+        if (it == 0) BQQ_MARK(3, 1u);       // first stage landed
         tc_fence_after();
         const uint64_t adesc = make_smem_desc(smem_u32(sA + s * kABytes));
         const uint64_t bdesc = make_smem_desc(smem_u32(sB + s * kBBytes));
 #pragma unroll
         for (int k = 0; k < kBK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units per step
           tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc, (it | k) != 0 ? 1u : 0u);
+        if (it == 0) BQQ_MARK(4, 1u);       // first MMAs issued
         tc_commit(empty_bar + s);            // frees the stage when these MMAs have read it
+        if (it == 0) BQQ_MARK(5, 1u);       // first commit issued
       }
       tc_commit(acc_bar);                    // accumulator complete (or abandoned)
+      BQQ_MARK(6, 1u);
     }
   } else {
     // epilogue warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31
     const int quarter = warp & 3;
     const bool ok = mbar_wait(acc_bar, 0) && !*failed;
     if (!ok) *failed = 1;
+    if (warp == 2 && lane == 0) BQQ_MARK(7, ok ? 1u : 2u);   // accumulator barrier passed
     tc_fence_after();
     if (ok) {
-      const float inv_scale = 1.f / w_scale_from_trailer(p.trailer, p.bound_mult);
+      const float inv_scale = p.trailer ? 1.f / w_scale_from_trailer(p.trailer, p.bound_mult) : 1.f;
       const int m = m0 + quarter * 32 + lane;
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
         tc_wait_ld();
+        if (c == 0 && warp == 2 && lane == 0) BQQ_MARK(8, 1u);   // first tensor-memory load done
         const int nb = n0 + c * 32;
         if (m < p.M && nb < p.N) {
           const size_t row = (size_t)m * p.ldy;
@@ -244,8 +262,10 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    if (lane == 0) BQQ_MARK(9, 1u);
   }
   if (threadIdx.x == 0 && *failed) atomicExch(p.status, 1u);
+#undef BQQ_MARK
 }
 
 // ---- x staging: any dtype / stride -> dense 16-bit rows (hi, lo for fp32) ----
@@ -304,12 +324,14 @@ static int make_map(CUtensorMap* map, const void* ptr, bool bf16, uint64_t rows,
 
 static inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
-// workspace: [status 256 B][W fp16 N x K][x hi M x K][x lo M x K]
+// workspace: [status 256 B][W parts 2 x N x K 16-bit][x hi M x K][x lo M x K]
 size_t prefill_workspace_bytes(const BqqDims* dims, int M) {
   Geom g(*dims);
   const size_t K = g.in_features();
-  return 256 + up256((size_t)g.out_features() * K * 2) + 2 * up256((size_t)M * K * 2);
+  return 256 + up256((size_t)2 * g.out_features() * K * 2) + 2 * up256((size_t)M * K * 2);
 }
+
+static volatile unsigned* g_gemm_dbg = nullptr;   // set only by the probe entry point below
 
 template <int BN>
 static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
@@ -332,22 +354,23 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   if (((uintptr_t)ws & 255) != 0) return BQQ_ERR_MISALIGNED;
   uint8_t* wsb = reinterpret_cast<uint8_t*>(ws);
   unsigned* status = reinterpret_cast<unsigned*>(wsb);
-  uint16_t* W = reinterpret_cast<uint16_t*>(wsb + 256);
-  uint16_t* xhi = reinterpret_cast<uint16_t*>(wsb + 256 + up256((size_t)N * K * 2));
+  uint16_t* W = reinterpret_cast<uint16_t*>(wsb + 256);              // [2][N][K]: hi rows, then lo rows
+  uint16_t* xhi = reinterpret_cast<uint16_t*>(wsb + 256 + up256((size_t)2 * N * K * 2));
   uint16_t* xlo = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(xhi) + up256((size_t)M * K * 2));
   const float* trailer = L->coef + g.coef_records() * 4;   // written by bqq_pack_coeffs
 
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return BQQ_ERR_CUDA;
 
-  // 1. dense W (fp16, scaled by the power of two derived from the bound) into scratch
-  int rc = reconstruct_launch_dev(L, W, BQQ_F16, 1.f, trailer, st);
+  // 1. dense W into scratch, in the activations' 16-bit format
+  const bool f16 = x_dtype == BQQ_F16;
+  int rc = f16 ? reconstruct_launch_dev(L, W, nullptr, BQQ_F16, 1.f, trailer, st)
+               : reconstruct_launch_dev(L, W, W + (size_t)N * K, BQQ_BF16, 1.f, nullptr, st);
   if (rc) return rc;
 
   // 2. x: used in place when it is a 16-bit tensor with TMA-compatible pitch, else staged
   const bool direct = x_dtype != BQQ_F32 && (ldx % 8) == 0 && ((uintptr_t)x & 15) == 0;
   const void* a_ptr = x;
   int64_t a_ld = ldx;
-  int passes = 1;
   if (!direct) {
     size_t n = (size_t)M * K;
     int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
@@ -356,28 +379,41 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
     if (rc) return rc;
     a_ptr = xhi;
     a_ld = K;
-    passes = x_dtype == BQQ_F32 ? 2 : 1;
   }
-  const bool a_bf16 = x_dtype != BQQ_F16;   // fp32 input is staged as bf16 hi + lo
+  const bool split_x = x_dtype == BQQ_F32;
 
   const int BN = (N >= 256) ? 256 : 128;
   CUtensorMap ma0, ma1, mb;
-  rc = make_map(&ma0, a_ptr, a_bf16, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, kBM);
+  rc = make_map(&ma0, a_ptr, !f16, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, kBM);
   if (rc) return rc;
-  rc = make_map(&ma1, passes == 2 ? (const void*)xlo : a_ptr, a_bf16, (uint64_t)M, (uint64_t)K,
-                passes == 2 ? (uint64_t)K : (uint64_t)a_ld, kBM);
+  rc = make_map(&ma1, split_x ? (const void*)xlo : a_ptr, !f16, (uint64_t)M, (uint64_t)K,
+                split_x ? (uint64_t)K : (uint64_t)a_ld, kBM);
   if (rc) return rc;
-  rc = make_map(&mb, W, false, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)BN);
+  rc = make_map(&mb, W, !f16, (uint64_t)(f16 ? N : 2 * N), (uint64_t)K, (uint64_t)K, (uint32_t)BN);
   if (rc) return rc;
 
   GemmParams p;
-  p.y = y; p.bias = L->bias; p.trailer = trailer; p.bound_mult = (float)(g.bw * g.r); p.status = status;
+  p.y = y; p.bias = L->bias; p.trailer = f16 ? trailer : nullptr; p.bound_mult = (float)(g.bw * g.r);
+  p.status = status;
   p.ldy = ldy; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
-  p.M = M; p.N = N; p.K = K; p.a_passes = passes;
-  // instruction descriptor: fp32 accumulate, A format, B = fp16, both K-major, N and M extents
-  p.idesc = (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | (0u << 10) | ((uint32_t)(BN >> 3) << 17) |
-            ((uint32_t)(kBM >> 4) << 24);
+  p.M = M; p.N = N; p.K = K;
+  p.dbg = g_gemm_dbg;
+  for (int i = 0; i < 3; ++i) { p.a_sel[i] = 0; p.b_row[i] = 0; }
+  if (f16) {
+    p.passes = 1;
+  } else if (!split_x) {
+    p.passes = 2; p.b_row[1] = N;                       // x*Whi + x*Wlo
+  } else {
+    p.passes = 3; p.b_row[1] = N; p.a_sel[2] = 1;       // xhi*Whi + xhi*Wlo + xlo*Whi
+  }
+  // instruction descriptor: fp32 accumulate, A and B in the same 16-bit format, both K-major
+  const uint32_t fmt = f16 ? 0u : 1u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
   return BN == 256 ? launch_gemm<256>(ma0, ma1, mb, p, st) : launch_gemm<128>(ma0, ma1, mb, p, st);
 }
 
 }  // namespace bqq
+
+// Probe hook (not part of the public header): progress markers of the GEMM kernel's first CTA
+// are written to `host_mapped` (device-visible pinned host memory, >= 16 words) when non-NULL.
+extern "C" void bqq_debug_set_gemm_markers(volatile unsigned* host_mapped) { bqq::g_gemm_dbg = host_mapped; }

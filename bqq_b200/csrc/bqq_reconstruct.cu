@@ -17,6 +17,7 @@ struct ReconParams {
   const uint32_t* yp;
   const float4* coef;
   void* W;
+  void* W_lo;               // optional second part: W - round(W), same type and layout
   const float* trailer;     // optional coefficient trailer: entries are also scaled by w_scale_from_trailer
   float scale;
   int w_dtype;
@@ -82,18 +83,23 @@ bqq_reconstruct_kernel(const ReconParams p) {
         acc = fmaf(co.x, (float)core, acc);
         acc = fmaf(co.y, (float)ys, acc);
       }
-      if (q < p.Q) store_from_float(p.W, (size_t)(i * p.P + pp) * ldw + (size_t)j * p.Q + q, p.w_dtype, acc * scale);
+      if (q < p.Q) {
+        const size_t at = (size_t)(i * p.P + pp) * ldw + (size_t)j * p.Q + q;
+        const float w = acc * scale;
+        store_from_float(p.W, at, p.w_dtype, w);
+        if (p.W_lo) store_from_float(p.W_lo, at, p.w_dtype, w - load_as_float(p.W, at, p.w_dtype));
+      }
     }
     __syncwarp();
   }
 }
 
-int reconstruct_launch_dev(const BqqLayer* L, void* W, int w_dtype, float scale, const float* trailer,
+int reconstruct_launch_dev(const BqqLayer* L, void* W, void* W_lo, int w_dtype, float scale, const float* trailer,
                            cudaStream_t st) {
   Geom g(L->dims);
   ReconParams p;
   p.zp = L->zplanes; p.yp = L->yplanes; p.coef = reinterpret_cast<const float4*>(L->coef);
-  p.W = W; p.scale = scale; p.trailer = trailer; p.w_dtype = w_dtype;
+  p.W = W; p.W_lo = W_lo; p.scale = scale; p.trailer = trailer; p.w_dtype = w_dtype;
   p.bw = g.bw; p.rw = g.rw; p.cw = g.cw; p.P = g.P; p.Q = g.Q; p.r = g.r;
   p.QW = g.QW; p.RW = g.RW; p.RP = g.RP; p.PP = g.PP; p.NS = g.NS;
   p.total_tasks = (long long)g.rw * g.cw * g.QW;
@@ -106,7 +112,7 @@ int reconstruct_launch_dev(const BqqLayer* L, void* W, int w_dtype, float scale,
 }
 
 int reconstruct_launch(const BqqLayer* L, void* W, int w_dtype, float scale, cudaStream_t st) {
-  return reconstruct_launch_dev(L, W, w_dtype, scale, nullptr, st);
+  return reconstruct_launch_dev(L, W, nullptr, w_dtype, scale, nullptr, st);
 }
 
 }  // namespace bqq
