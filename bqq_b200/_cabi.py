@@ -17,9 +17,9 @@ DECODE_MAX_M = 16
 
 EXPORTS = [
     'bqq_abi_version', 'bqq_strerror', 'bqq_device_supported',
-    'bqq_zplane_words', 'bqq_yplane_words', 'bqq_coeff_floats', 'bqq_algorithmic_bytes',
+    'bqq_zplane_words', 'bqq_yplane_words', 'bqq_algorithmic_bytes',
     'bqq_pack_planes', 'bqq_unpack_planes', 'bqq_pack_planes_host', 'bqq_unpack_planes_host',
-    'bqq_repack_u8_planes', 'bqq_pack_coeffs',
+    'bqq_repack_u8_planes',
     'bqq_decode_workspace_bytes', 'bqq_forward_decode',
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
@@ -32,8 +32,8 @@ class BqqDims(C.Structure):
 
 class BqqLayer(C.Structure):
     _fields_ = [('dims', BqqDims), ('zplanes', C.c_void_p), ('yplanes', C.c_void_p),
-                ('coef', C.c_void_p), ('bias', C.c_void_p), ('bias_dtype', C.c_int32),
-                ('reserved', C.c_int32)]
+                ('a', C.c_void_p), ('b', C.c_void_p), ('c', C.c_void_p), ('d', C.c_void_p),
+                ('bias', C.c_void_p), ('coef_dtype', C.c_int32), ('bias_dtype', C.c_int32)]
 
 
 def _load():
@@ -49,13 +49,12 @@ def _load():
         'bqq_strerror': (C.c_char_p, [i32]),
         'bqq_device_supported': (C.c_int, []),
         'bqq_zplane_words': (sz, [dp]), 'bqq_yplane_words': (sz, [dp]),
-        'bqq_coeff_floats': (sz, [dp]), 'bqq_algorithmic_bytes': (sz, [dp]),
+        'bqq_algorithmic_bytes': (sz, [dp]),
         'bqq_pack_planes': (i32, [vp, vp, dp, vp, vp, vp, vp, vp]),
         'bqq_unpack_planes': (i32, [vp, vp, dp, vp, vp, vp]),
         'bqq_pack_planes_host': (i32, [vp, vp, dp, vp, vp, vp, vp]),
         'bqq_unpack_planes_host': (i32, [vp, vp, dp, vp, vp]),
-        'bqq_repack_u8_planes': (i32, [vp, vp, dp, vp, vp, vp]),
-        'bqq_pack_coeffs': (i32, [vp, vp, vp, vp, i32, dp, vp, vp]),
+        'bqq_repack_u8_planes': (i32, [vp, vp, dp, vp, vp, vp, vp, vp]),
         'bqq_decode_workspace_bytes': (sz, [dp, i32]),
         'bqq_prefill_workspace_bytes': (sz, [dp, i32]),
         'bqq_forward_workspace_bytes': (sz, [dp, i32]),

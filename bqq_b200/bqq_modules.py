@@ -44,17 +44,14 @@ def _workspace(device: torch.device, kind: str, nbytes: int) -> torch.Tensor:
 
 
 class _PackedState:
-    """Derived, non-persistent device state of one layer: bit planes, row sums
-    and fp32 coefficient records, rebuilt when the source tensors change."""
+    """Derived, non-persistent device state of one layer: bit planes and row sums,
+    rebuilt when the source buffers change.  Coefficients are not cached: the
+    kernels read the parameter tensors themselves on every call."""
 
-    __slots__ = ('plane_key', 'coef_key', 'dims', 'zplanes', 'yplanes', 'ysum', 'zsum', 'coef',
-                 'bias_key', 'layer')
+    __slots__ = ('plane_key', 'dims', 'zplanes', 'yplanes', 'ysum', 'zsum')
 
     def __init__(self):
         self.plane_key = None
-        self.coef_key = None
-        self.bias_key = None
-        self.layer = None
 
 
 def _tensor_key(t: torch.Tensor):
@@ -102,39 +99,47 @@ class _BqqForwardMixin:
                 if not lib.bqq_device_supported():
                     raise RuntimeError('bqq_b200: the current GPU is not an sm_100 device')
                 st.dims = self._dims()
-                st.zplanes = torch.empty(lib.bqq_zplane_words(st.dims), dtype=torch.int32, device=device)
-                st.yplanes = torch.empty(lib.bqq_yplane_words(st.dims), dtype=torch.int32, device=device)
+                nz, ny = lib.bqq_zplane_words(st.dims), lib.bqq_yplane_words(st.dims)
+                if nz == 0 or ny == 0:
+                    raise RuntimeError('bqq_b200: unsupported patch geometry '
+                                       f'(P={self.y_row}, Q={self.z_col}, r={self.inter_dimension})')
+                st.zplanes = torch.empty(nz, dtype=torch.int32, device=device)
+                st.yplanes = torch.empty(ny, dtype=torch.int32, device=device)
+                n = self.bit_width * self.row_width * self.col_width
+                st.ysum = torch.empty(n * self.y_row, dtype=torch.uint8, device=device)
+                st.zsum = torch.empty(n * self.z_col, dtype=torch.uint8, device=device)
                 self._build_planes(st, device)
             st.plane_key = pkey
-            st.coef_key = None
-            st.layer = None
-        ckey = tuple(_tensor_key(getattr(self, n)) for n in 'abcd')
-        if st.coef_key != ckey:
-            dt = self.a.dtype
-            if dt not in _DTYPE_CODE or any(getattr(self, n).dtype != dt for n in 'bcd'):
-                raise RuntimeError(f'bqq_b200: coefficients must share one of fp32/bf16/fp16, got {dt}')
-            with torch.cuda.device(device):
-                st.coef = torch.empty(lib.bqq_coeff_floats(st.dims), dtype=torch.float32, device=device)
-                a, b, c, d = (getattr(self, n).detach().contiguous() for n in 'abcd')
-                for t in (a, b, c, d):
-                    _require_cuda(t, 'a coefficient tensor')
-                check(lib.bqq_pack_coeffs(a.data_ptr(), b.data_ptr(), c.data_ptr(), d.data_ptr(),
-                                          _DTYPE_CODE[dt], st.dims, st.coef.data_ptr(),
-                                          torch.cuda.current_stream(device).cuda_stream), 'bqq_pack_coeffs')
-            st.coef_key = ckey
-            st.layer = None
-        bias = getattr(self, 'bias', None)
-        bkey = _tensor_key(bias) if bias is not None else None
-        if st.layer is None or st.bias_key != bkey:
-            if bias is not None:
-                _require_cuda(bias, 'the bias')
-                if bias.dtype not in _DTYPE_CODE:
-                    raise RuntimeError(f'bqq_b200: unsupported bias dtype {bias.dtype}')
-            st.layer = BqqLayer(st.dims, st.zplanes.data_ptr(), st.yplanes.data_ptr(), st.coef.data_ptr(),
-                                bias.data_ptr() if bias is not None else None,
-                                _DTYPE_CODE[bias.dtype] if bias is not None else 0, 0)
-            st.bias_key = bkey
         return st
+
+    def _layer(self, st: _PackedState) -> BqqLayer:
+        """Descriptor handed to the C ABI; coefficient pointers are the live parameters."""
+        coefs = []
+        dt = self.a.dtype
+        if dt not in _DTYPE_CODE:
+            raise RuntimeError(f'bqq_b200: coefficients must be fp32, bf16 or fp16, got {dt}')
+        for n in 'abcd':
+            t = getattr(self, n).detach()
+            _require_cuda(t, f'coefficient {n}')
+            if t.dtype != dt:
+                raise RuntimeError('bqq_b200: coefficients a, b, c, d must share one dtype')
+            if not t.is_contiguous():
+                t = t.contiguous()
+            coefs.append(t)
+        bias = getattr(self, 'bias', None)
+        if bias is not None:
+            bias = bias.detach()
+            _require_cuda(bias, 'the bias')
+            if bias.dtype not in _DTYPE_CODE:
+                raise RuntimeError(f'bqq_b200: unsupported bias dtype {bias.dtype}')
+            if not bias.is_contiguous():
+                bias = bias.contiguous()
+        layer = BqqLayer(st.dims, st.zplanes.data_ptr(), st.yplanes.data_ptr(),
+                         coefs[0].data_ptr(), coefs[1].data_ptr(), coefs[2].data_ptr(), coefs[3].data_ptr(),
+                         bias.data_ptr() if bias is not None else None,
+                         _DTYPE_CODE[dt], _DTYPE_CODE[bias.dtype] if bias is not None else 0)
+        layer._keepalive = (coefs, bias)
+        return layer
 
     # -- forward ------------------------------------------------------------
     def _check_inference_only(self, X) -> None:
@@ -166,19 +171,20 @@ class _BqqForwardMixin:
         if M == 0:
             return y.reshape(*X.shape[:-1], out_f)
         code = _DTYPE_CODE[X.dtype]
+        layer = self._layer(st)
         with torch.cuda.device(device):
             stream = torch.cuda.current_stream(device).cuda_stream
             # up to 16 rows: bit-streaming decode kernel; more: tensor-core prefill path
             if M <= _cabi.DECODE_MAX_M:
                 nbytes = lib.bqq_decode_workspace_bytes(st.dims, M)
                 ws = _workspace(device, 'decode', nbytes)
-                check(lib.bqq_forward_decode(st.layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(), code,
+                check(lib.bqq_forward_decode(layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(), code,
                                              y.stride(0), ws.data_ptr(), ws.numel(), stream),
                       'bqq_forward_decode')
             else:
                 nbytes = lib.bqq_prefill_workspace_bytes(st.dims, M)
                 ws = _workspace(device, 'prefill', nbytes)
-                check(lib.bqq_forward_prefill(st.layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(),
+                check(lib.bqq_forward_prefill(layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(),
                                               code, y.stride(0), ws.data_ptr(), ws.numel(), stream),
                       'bqq_forward_prefill')
         return y.reshape(*X.shape[:-1], out_f)
@@ -190,7 +196,7 @@ class _BqqForwardMixin:
         in_f = self.col_width * self.z_col
         W = torch.empty((out_f, in_f), dtype=dtype, device=device)
         with torch.cuda.device(device):
-            check(lib.bqq_reconstruct_weight(st.layer, W.data_ptr(), _DTYPE_CODE[dtype], 1.0,
+            check(lib.bqq_reconstruct_weight(self._layer(st), W.data_ptr(), _DTYPE_CODE[dtype], 1.0,
                                              torch.cuda.current_stream(device).cuda_stream),
                   'bqq_reconstruct_weight')
         return W
@@ -227,9 +233,6 @@ class BinaryQuadratic(_BqqForwardMixin, nn.Module):
         Z = self.Z.contiguous()
         if Y.dtype != torch.bool or Z.dtype != torch.bool:
             Y, Z = Y > 0.5, Z > 0.5
-        n = self.bit_width * self.row_width * self.col_width
-        st.ysum = torch.empty(n * self.y_row, dtype=torch.uint8, device=device)
-        st.zsum = torch.empty(n * self.z_col, dtype=torch.uint8, device=device)
         check(lib.bqq_pack_planes(Y.data_ptr(), Z.data_ptr(), st.dims, st.zplanes.data_ptr(),
                                   st.yplanes.data_ptr(), st.ysum.data_ptr(), st.zsum.data_ptr(),
                                   torch.cuda.current_stream(device).cuda_stream), 'bqq_pack_planes')
@@ -310,10 +313,10 @@ class PackedBinaryQuadratic(_BqqForwardMixin, nn.Module):
         return self.Y_packed, self.Z_packed
 
     def _build_planes(self, st, device):
-        st.ysum = st.zsum = None
         check(lib.bqq_repack_u8_planes(self.Y_packed.contiguous().data_ptr(),
                                        self.Z_packed.contiguous().data_ptr(), st.dims,
                                        st.zplanes.data_ptr(), st.yplanes.data_ptr(),
+                                       st.ysum.data_ptr(), st.zsum.data_ptr(),
                                        torch.cuda.current_stream(device).cuda_stream), 'bqq_repack_u8_planes')
 
     def get_weight(self, dtype=torch.float32):

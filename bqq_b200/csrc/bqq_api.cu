@@ -7,9 +7,9 @@ static int check_layer(const BqqLayer* L) {
   if (!L) return BQQ_ERR_NULL;
   int rc = check_dims(&L->dims);
   if (rc) return rc;
-  if (!L->zplanes || !L->yplanes || !L->coef) return BQQ_ERR_NULL;
-  if (((uintptr_t)L->zplanes & 15) || ((uintptr_t)L->yplanes & 15) || ((uintptr_t)L->coef & 15))
-    return BQQ_ERR_MISALIGNED;
+  if (!L->zplanes || !L->yplanes || !L->a || !L->b || !L->c || !L->d) return BQQ_ERR_NULL;
+  if (((uintptr_t)L->zplanes & 15) || ((uintptr_t)L->yplanes & 15)) return BQQ_ERR_MISALIGNED;
+  if (!dtype_size(L->coef_dtype)) return BQQ_ERR_DTYPE;
   if (L->bias && !dtype_size(L->bias_dtype)) return BQQ_ERR_DTYPE;
   return BQQ_OK;
 }
@@ -103,7 +103,7 @@ int bqq_reconstruct_weight(const BqqLayer* layer, void* W, int w_dtype, float sc
   if (rc) return rc;
   if (!W) return BQQ_ERR_NULL;
   if (!dtype_size(w_dtype)) return BQQ_ERR_DTYPE;
-  return reconstruct_launch(layer, W, w_dtype, scale, (cudaStream_t)stream);
+  return reconstruct_launch(layer, W, nullptr, w_dtype, scale, nullptr, (cudaStream_t)stream);
 }
 
 }  // extern "C"

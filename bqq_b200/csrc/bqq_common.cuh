@@ -1,4 +1,5 @@
-// Shared geometry, element-type helpers and launch checks for the bqq_b200 kernels.
+// Shared geometry, plane-layout arithmetic, element-type helpers and launch
+// checks for the bqq_b200 kernels.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -10,33 +11,52 @@
 
 namespace bqq {
 
-constexpr int kGroup = 4;  // patch-bits interleaved in one 128-bit lane load
+constexpr int kGroup = 4;  // col patches interleaved in one 128-bit lane load
 
 // Derived sizes of the packed planes of one layer.
+//
+// Patches are padded to PT x QT x RT blocks of 32 (rows of Y, columns of Z,
+// rank).  For a row patch i the super-group s = b*JG + jg holds col patches
+// j = 4*jg + sub of bit layer b.  Word order:
+//   Z [rw][NS][RT][QT][32 lanes][4 sub]     Y [rw][NS][PT][RT][32 lanes][4 sub]
+// Lane = 4*g + t.  Bits inside a word (fragment order of the int8 tensor-core
+// operand the decode kernel expands with byte masks):
+//   Z bit 8e + 4qh + rr = Z[k = 32rt + g + 8rr][q = 32qt + 16qh + 4t + e]
+//   Y bit 8e + 4kh + rr = Y[p = 32pt + g + 8rr][k = 32rt + 16kh + 4t + e]
 struct Geom {
   int bw, rw, cw, P, Q, r;
-  int QW, RW, RP, PP;  // words per Z row / Y row, padded Z rows / Y rows
-  int NPB, NS;         // patch-bits per row patch, super-groups per row patch
+  int PT, QT, RT;      // 32-blocks of P, Q, r
+  int JG, NS;          // col-patch groups per bit layer, super-groups per row patch
   __host__ __device__ Geom() {}
   __host__ __device__ explicit Geom(const BqqDims& d)
       : bw(d.bw), rw(d.rw), cw(d.cw), P(d.P), Q(d.Q), r(d.r) {
-    QW = (Q + 31) / 32;
-    RW = (r + 31) / 32;
-    RP = RW * 32;
-    PP = ((P + 31) / 32) * 32;
-    NPB = cw * bw;
-    NS = (NPB + kGroup - 1) / kGroup;
+    PT = (P + 31) / 32;
+    QT = (Q + 31) / 32;
+    RT = (r + 31) / 32;
+    JG = (cw + kGroup - 1) / kGroup;
+    NS = bw * JG;
   }
-  __host__ __device__ size_t z_words_per_sg() const { return (size_t)QW * RP * kGroup; }
-  __host__ __device__ size_t y_words_per_sg() const { return (size_t)RW * PP * kGroup; }
-  __host__ __device__ size_t z_words() const { return (size_t)rw * NS * z_words_per_sg(); }
-  __host__ __device__ size_t y_words() const { return (size_t)rw * NS * y_words_per_sg(); }
-  // per patch-bit records (a,b,c,d) followed by a 4-float trailer:
-  // [0] = max(|a|+|b|+|c|), [1] = max|d| over the layer (bound on |W| = bw*r*[0] + [1])
-  __host__ __device__ size_t coef_records() const { return (size_t)rw * NS * kGroup; }
-  __host__ __device__ size_t coef_floats() const { return coef_records() * 4 + 4; }
+  __host__ __device__ size_t z_words() const { return (size_t)rw * NS * RT * QT * 32 * kGroup; }
+  __host__ __device__ size_t y_words() const { return (size_t)rw * NS * PT * RT * 32 * kGroup; }
   __host__ __device__ int out_features() const { return rw * P; }
   __host__ __device__ int in_features() const { return cw * Q; }
+
+  // word offset and bit position of Z[b,i,j][k][q]
+  __host__ __device__ size_t z_word(int b, int i, int j, int k, int q, int* bit) const {
+    const int rt = k >> 5, rr = (k >> 3) & 3, g = k & 7;
+    const int qt = q >> 5, qh = (q >> 4) & 1, t = (q >> 2) & 3, e = q & 3;
+    *bit = 8 * e + 4 * qh + rr;
+    const size_t s = (size_t)b * JG + j / kGroup;
+    return (((((size_t)i * NS + s) * RT + rt) * QT + qt) * 32 + (4 * g + t)) * kGroup + (j % kGroup);
+  }
+  // word offset and bit position of Y[b,i,j][p][k]
+  __host__ __device__ size_t y_word(int b, int i, int j, int p, int k, int* bit) const {
+    const int pt = p >> 5, rr = (p >> 3) & 3, g = p & 7;
+    const int rt = k >> 5, kh = (k >> 4) & 1, t = (k >> 2) & 3, e = k & 3;
+    *bit = 8 * e + 4 * kh + rr;
+    const size_t s = (size_t)b * JG + j / kGroup;
+    return (((((size_t)i * NS + s) * PT + pt) * RT + rt) * 32 + (4 * g + t)) * kGroup + (j % kGroup);
+  }
 };
 
 inline int check_dims(const BqqDims* d) {
@@ -57,11 +77,22 @@ inline int dtype_size(int dt) {
   }
 }
 
-// Load one element of type code `dt` as float.
+// Load one element of type code `dt` as float.  Plain loads on purpose: a read-only
+// (__ldg) load may be hoisted above the guard that protects it, and callers guard
+// optional (possibly NULL) pointers and ragged edges with ordinary branches.
 __device__ __forceinline__ float load_as_float(const void* p, size_t idx, int dt) {
   if (dt == BQQ_F32) return reinterpret_cast<const float*>(p)[idx];
   if (dt == BQQ_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
   return __half2float(reinterpret_cast<const __half*>(p)[idx]);
+}
+
+// 128-bit streaming load of plane words (read once, keep out of L1).  Volatile asm so
+// that it stays behind the bounds test of its caller.
+__device__ __forceinline__ uint4 load_plane_u4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
 }
 
 __device__ __forceinline__ void store_from_float(void* p, size_t idx, int dt, float v) {
@@ -70,10 +101,17 @@ __device__ __forceinline__ void store_from_float(void* p, size_t idx, int dt, fl
   else reinterpret_cast<__half*>(p)[idx] = __float2half_rn(v);
 }
 
+// Round a value to the 16-bit type `dt` and back (used to split a weight into hi + lo parts).
+__device__ __forceinline__ float round_to(float v, int dt) {
+  if (dt == BQQ_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  if (dt == BQQ_F16) return __half2float(__float2half_rn(v));
+  return v;
+}
+
 // Power-of-two scale that maps a bound on |W| to at most 2^14 (fp16-safe range).
-// `trailer` is the 4-float tail of the coefficient buffer, mult = bw * r.
-__device__ __forceinline__ float w_scale_from_trailer(const float* trailer, float mult) {
-  const float bound = fmaf(mult, __ldg(trailer), __ldg(trailer + 1));
+// bound_parts = {max(|a|+|b|+|c|), max|d|}; |W| <= mult * parts[0] + parts[1], mult = bw * r.
+__device__ __forceinline__ float w_scale_from_bound(const float* bound_parts, float mult) {
+  const float bound = fmaf(mult, bound_parts[0], bound_parts[1]);
   if (!(bound > 0.f) || !isfinite(bound)) return 1.f;
   int e;
   frexpf(bound, &e);                 // bound = f * 2^e, f in [0.5, 1)
@@ -91,7 +129,9 @@ inline int launch_status() {
 int decode_launch(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                   int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t decode_workspace_bytes(const BqqDims* dims, int M);
-int reconstruct_launch(const BqqLayer* layer, void* W, int w_dtype, float scale, cudaStream_t stream);
+int reconstruct_launch(const BqqLayer* layer, void* W, void* W_lo, int w_dtype, float scale,
+                       const float* bound_parts, cudaStream_t stream);
+int coef_bound_launch(const BqqLayer* layer, float* bound_parts, cudaStream_t stream);
 int prefill_launch(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                    int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t prefill_workspace_bytes(const BqqDims* dims, int M);

@@ -21,9 +21,6 @@
 
 namespace bqq {
 
-int reconstruct_launch_dev(const BqqLayer* L, void* W, void* W_lo, int w_dtype, float scale, const float* trailer,
-                           cudaStream_t st);
-
 constexpr int kBM = 128;
 constexpr int kBK = 64;          // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int kStages = 4;
@@ -102,7 +99,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 struct GemmParams {
   void* y;
   const void* bias;
-  const float* trailer;      // coefficient trailer (bound on |W|)
+  const float* bound_parts;  // device {max(|a|+|b|+|c|), max|d|} when W was scaled (fp16), else NULL
   float bound_mult;          // bw * r
   unsigned* status;          // device word, set nonzero when a wait timed out
   int64_t ldy;
@@ -209,7 +206,7 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
     if (warp == 2 && lane == 0) BQQ_MARK(7, ok ? 1u : 2u);   // accumulator barrier passed
     tc_fence_after();
     if (ok) {
-      const float inv_scale = p.trailer ? 1.f / w_scale_from_trailer(p.trailer, p.bound_mult) : 1.f;
+      const float inv_scale = p.bound_parts ? 1.f / w_scale_from_bound(p.bound_parts, p.bound_mult) : 1.f;
       const int m = m0 + quarter * 32 + lane;
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -324,7 +321,7 @@ static int make_map(CUtensorMap* map, const void* ptr, bool bf16, uint64_t rows,
 
 static inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
-// workspace: [status 256 B][W parts 2 x N x K 16-bit][x hi M x K][x lo M x K]
+// workspace: [256 B: status word, bound parts at +16][W parts 2 x N x K 16-bit][x hi M x K][x lo M x K]
 size_t prefill_workspace_bytes(const BqqDims* dims, int M) {
   Geom g(*dims);
   const size_t K = g.in_features();
@@ -357,14 +354,20 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   uint16_t* W = reinterpret_cast<uint16_t*>(wsb + 256);              // [2][N][K]: hi rows, then lo rows
   uint16_t* xhi = reinterpret_cast<uint16_t*>(wsb + 256 + up256((size_t)2 * N * K * 2));
   uint16_t* xlo = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(xhi) + up256((size_t)M * K * 2));
-  const float* trailer = L->coef + g.coef_records() * 4;   // written by bqq_pack_coeffs
+  float* bound_parts = reinterpret_cast<float*>(wsb + 16);
 
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return BQQ_ERR_CUDA;
 
   // 1. dense W into scratch, in the activations' 16-bit format
   const bool f16 = x_dtype == BQQ_F16;
-  int rc = f16 ? reconstruct_launch_dev(L, W, nullptr, BQQ_F16, 1.f, trailer, st)
-               : reconstruct_launch_dev(L, W, W + (size_t)N * K, BQQ_BF16, 1.f, nullptr, st);
+  int rc;
+  if (f16) {
+    rc = coef_bound_launch(L, bound_parts, st);
+    if (rc) return rc;
+    rc = reconstruct_launch(L, W, nullptr, BQQ_F16, 1.f, bound_parts, st);
+  } else {
+    rc = reconstruct_launch(L, W, W + (size_t)N * K, BQQ_BF16, 1.f, nullptr, st);
+  }
   if (rc) return rc;
 
   // 2. x: used in place when it is a 16-bit tensor with TMA-compatible pitch, else staged
@@ -393,7 +396,7 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   if (rc) return rc;
 
   GemmParams p;
-  p.y = y; p.bias = L->bias; p.trailer = f16 ? trailer : nullptr; p.bound_mult = (float)(g.bw * g.r);
+  p.y = y; p.bias = L->bias; p.bound_parts = f16 ? bound_parts : nullptr; p.bound_mult = (float)(g.bw * g.r);
   p.status = status;
   p.ldy = ldy; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
   p.M = M; p.N = N; p.K = K;

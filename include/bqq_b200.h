@@ -58,18 +58,24 @@ typedef struct BqqDims {
 } BqqDims;
 
 /*
- * One packed layer (or one rank's shard of it: a shard is simply a layer with
- * fewer row patches).  Planes and coefficients are in this library's packed
- * formats (see bqq_pack_planes / bqq_pack_coeffs).
+ * One layer (or one rank's shard of it: a shard is simply a layer with fewer row
+ * patches).  The binary factors are in this library's packed plane format
+ * (bqq_pack_planes); the coefficients are read where the module keeps them:
+ * the parameter tensors a, b, c [bw,rw,cw] and d [rw,cw] of the reference
+ * (src/bqq_modules.py:28-31), contiguous, all of element type coef_dtype.  They
+ * are read on every call, so in-place updates of the parameters are always seen.
  */
 typedef struct BqqLayer {
   BqqDims dims;
-  const uint32_t* zplanes;   /* bqq_zplane_words() words                     */
-  const uint32_t* yplanes;   /* bqq_yplane_words() words                     */
-  const float*    coef;      /* bqq_coeff_floats() floats                    */
+  const uint32_t* zplanes;   /* bqq_zplane_words() words, 16-byte aligned    */
+  const uint32_t* yplanes;   /* bqq_yplane_words() words, 16-byte aligned    */
+  const void*     a;         /* [bw,rw,cw]                                   */
+  const void*     b;         /* [bw,rw,cw]                                   */
+  const void*     c;         /* [bw,rw,cw]                                   */
+  const void*     d;         /* [rw,cw]                                      */
   const void*     bias;      /* [rw*P] or NULL                               */
+  int32_t         coef_dtype;
   int32_t         bias_dtype;
-  int32_t         reserved;
 } BqqLayer;
 
 int         bqq_abi_version(void);
@@ -81,21 +87,26 @@ int bqq_device_supported(void);
 /* ---- packed sizes (host, pure arithmetic) -------------------------------- */
 size_t bqq_zplane_words(const BqqDims* dims);
 size_t bqq_yplane_words(const BqqDims* dims);
-size_t bqq_coeff_floats(const BqqDims* dims);
 /* bits + fp32 coefficients actually carrying information, in bytes */
 size_t bqq_algorithmic_bytes(const BqqDims* dims);
 
 /* ---- load-time packer -----------------------------------------------------
  * Replaces PackedBinaryQuadratic.from_unpacked / _np_packbits
  * (src/bqq_modules.py:99-148): bool Y [bw,rw,cw,P,r] and Z [bw,rw,cw,r,Q]
- * (one byte per entry, 0/1) become 32-bit bit planes
- *   zplanes [rw][NS][QW][RP][4]  bit q%32 of word q/32 of Z row k
- *   yplanes [rw][NS][RW][PP][4]  bit k%32 of word k/32 of Y row p
- * where a patch-bit n = j*bw+b, NS = ceil(cw*bw/4) super-groups of 4
- * patch-bits (innermost index), QW = ceil(Q/32), RW = ceil(r/32),
- * RP/PP = r/P rounded up to 32; all padding is zero.  ysum [bw,rw,cw,P] and
- * zsum [bw,rw,cw,Q] (uint8; may be NULL) are the row sums of Y and column
- * sums of Z that the reference keeps as Y_sum_i16 / Z_sum_i16 (:140-141).
+ * (one byte per entry, 0/1) become 32-bit bit planes.  Patches are padded to
+ * PT x QT x RT blocks of 32 (P, Q, r rounded up); for a row patch i the
+ * super-group s = b*JG + jg (JG = ceil(cw/4), NS = bw*JG) holds the col patches
+ * j = 4*jg + sub of bit layer b, interleaved so that one 128-bit load fetches a
+ * word of all four:
+ *   zplanes [rw][NS][RT][QT][32 lanes][4 sub]
+ *   yplanes [rw][NS][PT][RT][32 lanes][4 sub]
+ * With lane = 4*g + t, a word is a 4-row x 8-column fragment in the order of the
+ * int8 tensor-core operand that the decode kernel builds from it with byte masks:
+ *   Z bit 8e + 4qh + rr = Z[k = 32rt + g + 8rr][q = 32qt + 16qh + 4t + e]
+ *   Y bit 8e + 4kh + rr = Y[p = 32pt + g + 8rr][k = 32rt + 16kh + 4t + e]
+ * All padding is zero.  ysum [bw,rw,cw,P] and zsum [bw,rw,cw,Q] (uint8; may be
+ * NULL) are the row sums of Y and column sums of Z that the reference keeps as
+ * Y_sum_i16 / Z_sum_i16 (:140-141).
  */
 int bqq_pack_planes(const uint8_t* Y_bool, const uint8_t* Z_bool, const BqqDims* dims,
                     uint32_t* zplanes, uint32_t* yplanes, uint8_t* ysum, uint8_t* zsum,
@@ -112,33 +123,32 @@ int bqq_unpack_planes_host(const uint32_t* zplanes, const uint32_t* yplanes, con
 /*
  * Re-pack the reference's own uint8 checkpoints (PackedBinaryQuadratic buffers
  * Y_packed [bw,rw,cw,P,ceil(r/8)], Z_packed [bw,rw,cw,Q,ceil(r/8)], big-endian,
- * Z transposed; src/bqq_modules.py:70-74) into bit planes.
+ * Z transposed; src/bqq_modules.py:70-74) into bit planes (ysum/zsum optional).
  */
 int bqq_repack_u8_planes(const uint8_t* Y_packed, const uint8_t* Z_packed, const BqqDims* dims,
-                         uint32_t* zplanes, uint32_t* yplanes, void* stream);
-
-/*
- * Coefficients a,b,c [bw,rw,cw] and d [rw,cw] (element type `dtype`) to
- * float32 [rw][NS*4][4] = (a, b, c, d if bit 0 else 0) per patch-bit.
- * Replaces the per-call reshape/.to(float32) of src/bqq_cuda.cu:318-323.
- */
-int bqq_pack_coeffs(const void* a, const void* b, const void* c, const void* d, int dtype,
-                    const BqqDims* dims, float* coef, void* stream);
+                         uint32_t* zplanes, uint32_t* yplanes, uint8_t* ysum, uint8_t* zsum,
+                         void* stream);
 
 /* ---- forward ---------------------------------------------------------------
  * y[M, rw*P] = x[M, cw*Q] @ W^T (+ bias), the result of
- * BinaryQuadratic.forward (src/bqq_modules.py:34-46), fp32 accumulation.
+ * BinaryQuadratic.forward (src/bqq_modules.py:34-46).
  * x rows are ldx elements apart, y rows ldy elements apart; x and y use the
  * same element type codes (y_dtype may differ from x_dtype).
  *
- * bqq_forward_decode: M <= BQQ_DECODE_MAX_M; streams the packed planes once;
- *   replaces bqq_forward_kernel (src/bqq_cuda.cu:47-180).  The workspace
- *   (bqq_decode_workspace_bytes, 256-byte aligned) must be zero-filled once
- *   after allocation; the kernel leaves it zeroed for the next call.  Calls
- *   sharing one workspace must not overlap on the GPU.
+ * bqq_forward_decode: M <= BQQ_DECODE_MAX_M; streams the packed planes once,
+ *   both contractions on the int8 tensor cores with x and the intermediate in
+ *   block fixed point (16 and 24 bits), fp32 across patches; replaces
+ *   bqq_forward_kernel (src/bqq_cuda.cu:47-180).  The first 256 KiB of the
+ *   workspace (bqq_decode_workspace_bytes, 256-byte aligned) are counters that
+ *   must be zero-filled once after allocation; the kernel leaves them zeroed,
+ *   so one workspace serves layers of any shape.  Calls sharing a workspace
+ *   must not overlap on the GPU.  Results do not depend on the number of row
+ *   patches: a row shard reproduces its slice of the full output bit for bit.
  * bqq_forward_prefill: any M; rebuilds W once into the workspace and runs a
- *   tcgen05 tensor-core GEMM; replaces reconstruct_W_kernel + torch::mm
- *   (src/bqq_cuda.cu:198-246, 367-383).
+ *   tcgen05 tensor-core GEMM (fp32 accumulate); replaces reconstruct_W_kernel +
+ *   torch::mm (src/bqq_cuda.cu:198-246, 367-383).  The first word of the
+ *   workspace is a status word: non-zero after the call completes means a
+ *   bounded device-side wait gave up (BQQ_ERR_TIMEOUT) and y is invalid.
  * bqq_forward: picks decode for M <= 16 and prefill otherwise, the dispatch
  *   of src/bqq_cuda.cu:327,367; workspace must satisfy bqq_forward_workspace_bytes.
  */

@@ -191,106 +191,76 @@ def popcount_matmul_u8(Yp, Zp):
 # ---------------------------------------------------------------------------
 # 32-bit bit-plane layout of this library (layout oracle for the GPU packer)
 # ---------------------------------------------------------------------------
+#
+# Patches are padded to multiples of 32 in P, Q and r (PT, QT, RT blocks of 32).
+# For one row patch i the patch-bits are ordered bit layer first: super-group
+# s = b*JG + jg holds the 4 col patches j = 4*jg + sub (JG = ceil(cw/4)); the 4
+# words of a super-group are adjacent so that one 128-bit load fetches them.
+#
+# Inside a 32x32 block a word belongs to a lane = 4*g + t (g = 0..7, t = 0..3)
+# and holds a 4-row x 8-column fragment arranged for the int8 tensor-core
+# operand that the decode kernel builds with byte masks:
+#   Z word bit 8*e + 4*qh + rr  =  Z[k = 32*rt + g + 8*rr][q = 32*qt + 16*qh + 4*t + e]
+#   Y word bit 8*e + 4*kh + rr  =  Y[p = 32*pt + g + 8*rr][k = 32*rt + 16*kh + 4*t + e]
+# Word order: Z [rw][NS][RT][QT][32 lanes][4 sub], Y [rw][NS][PT][RT][32][4].
 
-GROUP = 4  # patch-bits interleaved per 128-bit lane load
+GROUP = 4  # col patches interleaved per 128-bit lane load
 
 
 def plane_geometry(bw, rw, cw, P, Q, r):
-    """Sizes of the packed planes.
+    PT, QT, RT = (P + 31) // 32, (Q + 31) // 32, (r + 31) // 32
+    JG = (cw + GROUP - 1) // GROUP
+    return dict(PT=PT, QT=QT, RT=RT, JG=JG, NS=bw * JG)
 
-    A "patch-bit" is one (col patch j, bit b) pair of a row patch i, numbered
-    n = j*bw + b.  GROUP consecutive patch-bits form a super-group.
-    """
-    QW = (Q + 31) // 32           # words per Z row (bits over q)
-    RW = (r + 31) // 32           # words per Y row (bits over k)
-    RP = ((r + 31) // 32) * 32    # Z rows, padded to a lane multiple
-    PP = ((P + 31) // 32) * 32    # Y rows, padded to a lane multiple
-    NPB = cw * bw
-    NS = (NPB + GROUP - 1) // GROUP
-    return dict(QW=QW, RW=RW, RP=RP, PP=PP, NPB=NPB, NS=NS)
+
+_BITW = (1 << (8 * np.arange(4)[:, None, None] + 4 * np.arange(2)[None, :, None]
+               + np.arange(4)[None, None, :])).astype(np.uint64)      # [e][half][rr]
 
 
 def pack_planes_u32(Y, Z):
-    """Bit planes as the GPU packer must produce them.
+    """Bit planes as the GPU packer must produce them (see the layout note above).
 
-    Zp uint32 [rw, NS, QW, RP, 4]: word = bits q%32 (LSB first) of Z row k,
-        word index qw = q//32, for the 4 patch-bits of super-group s.
-    Yp uint32 [rw, NS, RW, PP, 4]: word = bits k%32 (LSB first) of Y row p.
-    ysum uint8 [bw,rw,cw,P], zsum uint8 [bw,rw,cw,Q]: row sums of Y over k and
-        column sums of Z over k (equal the reference's Y_sum_i16 / Z_sum_i16).
-    Padding rows/bits/patch-bits are zero.
+    Returns Zp uint32 [rw,NS,RT,QT,32,4], Yp uint32 [rw,NS,PT,RT,32,4],
+    ysum uint8 [bw,rw,cw,P] (row sums of Y over k) and zsum uint8 [bw,rw,cw,Q]
+    (column sums of Z over k; the reference's Y_sum_i16 / Z_sum_i16).
     """
     Y = np.asarray(Y).astype(bool)
     Z = np.asarray(Z).astype(bool)
     bw, rw, cw, P, r = Y.shape
     Q = Z.shape[-1]
     g = plane_geometry(bw, rw, cw, P, Q, r)
-    QW, RW, RP, PP, NS = g['QW'], g['RW'], g['RP'], g['PP'], g['NS']
-
-    def to_words(bits, nwords):
-        # bits [..., L] -> uint32 [..., nwords], LSB-first
-        L = bits.shape[-1]
-        padded = np.zeros(bits.shape[:-1] + (nwords * 32,), np.uint8)
-        padded[..., :L] = bits
-        by = np.packbits(padded, axis=-1, bitorder='little')
-        return np.ascontiguousarray(by).view('<u4').reshape(bits.shape[:-1] + (nwords,))
-
-    Zw = to_words(Z, QW)                      # [bw,rw,cw,r,QW]
-    Yw = to_words(Y, RW)                      # [bw,rw,cw,P,RW]
-    Zp = np.zeros((rw, NS * GROUP, QW, RP), np.uint32)
-    Yp = np.zeros((rw, NS * GROUP, RW, PP), np.uint32)
-    # n = j*bw + b
-    Zn = Zw.transpose(1, 2, 0, 4, 3).reshape(rw, cw * bw, QW, r)
-    Yn = Yw.transpose(1, 2, 0, 4, 3).reshape(rw, cw * bw, RW, P)
-    Zp[:, :cw * bw, :, :r] = Zn
-    Yp[:, :cw * bw, :, :P] = Yn
-    Zp = Zp.reshape(rw, NS, GROUP, QW, RP).transpose(0, 1, 3, 4, 2)
-    Yp = Yp.reshape(rw, NS, GROUP, RW, PP).transpose(0, 1, 3, 4, 2)
-    ysum = Y.sum(axis=-1).astype(np.uint8)
-    zsum = Z.sum(axis=-2).astype(np.uint8)
-    return np.ascontiguousarray(Zp), np.ascontiguousarray(Yp), ysum, zsum
+    PT, QT, RT, JG = g['PT'], g['QT'], g['RT'], g['JG']
+    Zf = np.zeros((bw, rw, JG * GROUP, RT * 32, QT * 32), np.uint64)
+    Yf = np.zeros((bw, rw, JG * GROUP, PT * 32, RT * 32), np.uint64)
+    Zf[:, :, :cw, :r, :Q] = Z
+    Yf[:, :, :cw, :P, :r] = Y
+    # rows = 32*blk + 8*rr + g ; cols = 32*blk + 16*half + 4*t + e
+    Zf = Zf.reshape(bw, rw, JG, GROUP, RT, 4, 8, QT, 2, 4, 4)     # b i jg sub rt rr g qt qh t e
+    Zf = Zf.transpose(1, 0, 2, 4, 7, 6, 9, 3, 10, 8, 5)           # i b jg rt qt g t sub e qh rr
+    Zp = (Zf * _BITW).sum(axis=(-1, -2, -3)).astype(np.uint32)
+    Yf = Yf.reshape(bw, rw, JG, GROUP, PT, 4, 8, RT, 2, 4, 4)     # b i jg sub pt rr g rt kh t e
+    Yf = Yf.transpose(1, 0, 2, 4, 7, 6, 9, 3, 10, 8, 5)           # i b jg pt rt g t sub e kh rr
+    Yp = (Yf * _BITW).sum(axis=(-1, -2, -3)).astype(np.uint32)
+    Zp = np.ascontiguousarray(Zp.reshape(rw, bw * JG, RT, QT, 32, GROUP))
+    Yp = np.ascontiguousarray(Yp.reshape(rw, bw * JG, PT, RT, 32, GROUP))
+    return Zp, Yp, Y.sum(axis=-1).astype(np.uint8), Z.sum(axis=-2).astype(np.uint8)
 
 
 def unpack_planes_u32(Zp, Yp, bw, rw, cw, P, Q, r):
     """Inverse of pack_planes_u32 -> bool Y [bw,rw,cw,P,r], Z [bw,rw,cw,r,Q]."""
     g = plane_geometry(bw, rw, cw, P, Q, r)
-    QW, RW, RP, PP, NS = g['QW'], g['RW'], g['RP'], g['PP'], g['NS']
-    Zp = np.asarray(Zp, np.uint32).reshape(rw, NS, QW, RP, GROUP)
-    Yp = np.asarray(Yp, np.uint32).reshape(rw, NS, RW, PP, GROUP)
-    Zn = Zp.transpose(0, 1, 4, 2, 3).reshape(rw, NS * GROUP, QW, RP)[:, :cw * bw, :, :r]
-    Yn = Yp.transpose(0, 1, 4, 2, 3).reshape(rw, NS * GROUP, RW, PP)[:, :cw * bw, :, :P]
-
-    def to_bits(words, L):
-        # words [..., nwords] -> bits [..., L]
-        by = np.ascontiguousarray(words.astype('<u4')).view(np.uint8)
-        bits = np.unpackbits(by, axis=-1, bitorder='little')
-        return bits[..., :L].astype(bool)
-
-    # Zn [rw, n, QW, r] -> [rw, cw, bw, r, QW]
-    Zw = Zn.reshape(rw, cw, bw, QW, r).transpose(2, 0, 1, 4, 3)
-    Yw = Yn.reshape(rw, cw, bw, RW, P).transpose(2, 0, 1, 4, 3)
-    Z = to_bits(np.ascontiguousarray(Zw), Q)
-    Y = to_bits(np.ascontiguousarray(Yw), r)
+    PT, QT, RT, JG = g['PT'], g['QT'], g['RT'], g['JG']
+    shifts = (8 * np.arange(4)[:, None, None] + 4 * np.arange(2)[None, :, None]
+              + np.arange(4)[None, None, :]).astype(np.uint32)    # [e][half][rr]
+    Zw = np.asarray(Zp, np.uint32).reshape(rw, bw, JG, RT, QT, 8, 4, GROUP)
+    Zb = (Zw[..., None, None, None] >> shifts) & 1                # i b jg rt qt g t sub e qh rr
+    Zb = Zb.transpose(1, 0, 2, 7, 3, 10, 5, 4, 9, 6, 8)           # b i jg sub rt rr g qt qh t e
+    Z = Zb.reshape(bw, rw, JG * GROUP, RT * 32, QT * 32)[:, :, :cw, :r, :Q].astype(bool)
+    Yw = np.asarray(Yp, np.uint32).reshape(rw, bw, JG, PT, RT, 8, 4, GROUP)
+    Yb = (Yw[..., None, None, None] >> shifts) & 1                # i b jg pt rt g t sub e kh rr
+    Yb = Yb.transpose(1, 0, 2, 7, 3, 10, 5, 4, 9, 6, 8)           # b i jg sub pt rr g rt kh t e
+    Y = Yb.reshape(bw, rw, JG * GROUP, PT * 32, RT * 32)[:, :, :cw, :P, :r].astype(bool)
     return Y, Z
-
-
-def pack_coefficients(a, b, c, d):
-    """float32 [rw, NS*4, 4]: (a, b, c, d if bit==0 else 0) per patch-bit
-    n = j*bw + b; padding patch-bits are all-zero."""
-    a = np.asarray(a, np.float32)[..., 0, 0]
-    b = np.asarray(b, np.float32)[..., 0, 0]
-    c = np.asarray(c, np.float32)[..., 0, 0]
-    d = np.asarray(d, np.float32)[..., 0, 0]
-    bw, rw, cw = a.shape
-    NS = (cw * bw + GROUP - 1) // GROUP
-    out = np.zeros((rw, NS * GROUP, 4), np.float32)
-    co = np.zeros((rw, cw, bw, 4), np.float32)
-    co[..., 0] = a.transpose(1, 2, 0)
-    co[..., 1] = b.transpose(1, 2, 0)
-    co[..., 2] = c.transpose(1, 2, 0)
-    co[:, :, 0, 3] = d
-    out[:, :cw * bw] = co.reshape(rw, cw * bw, 4)
-    return out
 
 
 def algorithmic_bytes(bw, rw, cw, P, Q, r):

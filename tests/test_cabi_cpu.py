@@ -43,9 +43,8 @@ def test_sizes(cabi, shape):
     bw, rw, cw, P, Q, r = shape
     d = cabi.dims(*shape)
     g = O.plane_geometry(bw, rw, cw, P, Q, r)
-    assert cabi.lib.bqq_zplane_words(d) == rw * g['NS'] * g['QW'] * g['RP'] * 4
-    assert cabi.lib.bqq_yplane_words(d) == rw * g['NS'] * g['RW'] * g['PP'] * 4
-    assert cabi.lib.bqq_coeff_floats(d) == rw * g['NS'] * 4 * 4 + 4
+    assert cabi.lib.bqq_zplane_words(d) == rw * g['NS'] * g['RT'] * g['QT'] * 32 * 4
+    assert cabi.lib.bqq_yplane_words(d) == rw * g['NS'] * g['PT'] * g['RT'] * 32 * 4
     assert cabi.lib.bqq_algorithmic_bytes(d) == O.algorithmic_bytes(bw, rw, cw, P, Q, r)
 
 
@@ -61,16 +60,17 @@ def test_bad_arguments_rejected_without_gpu(cabi):
     assert lib.bqq_pack_planes(None, p, ok, p, p, None, None, None) == -1          # NULL
     assert lib.bqq_pack_planes(p, p, bad, p, p, None, None, None) == -2            # bad shape
     assert lib.bqq_pack_planes(p, p, big, p, p, None, None, None) == -3            # unsupported
-    assert lib.bqq_pack_coeffs(p, p, p, p, 7, ok, p, None) == -6                   # dtype
-    layer = cabi.BqqLayer(ok, p, p, p, None, 0, 0)
+    layer = cabi.BqqLayer(ok, p, p, p, p, p, p, None, 0, 0)
     assert lib.bqq_forward_decode(layer, None, 0, 1, 32, p, 0, 32, None, 0, None) == -1
     assert lib.bqq_forward_decode(layer, p, 0, 0, 32, p, 0, 32, None, 0, None) == -2
     assert lib.bqq_forward_decode(layer, p, 0, 17, 32, p, 0, 32, None, 0, None) == -3
     assert lib.bqq_forward_decode(layer, p, 9, 1, 32, p, 0, 32, None, 0, None) == -6
     assert lib.bqq_forward_decode(layer, p, 0, 1, 16, p, 0, 32, None, 0, None) == -2   # ldx < in_features
-    mis = cabi.BqqLayer(ok, p + 4, p, p, None, 0, 0)
+    mis = cabi.BqqLayer(ok, p + 4, p, p, p, p, p, None, 0, 0)
     assert lib.bqq_forward_decode(mis, p, 0, 1, 32, p, 0, 32, None, 0, None) == -4
     assert lib.bqq_forward_prefill(layer, p, 0, 64, 32, p, 0, 32, None, 0, None) == -5  # workspace
+    baddt = cabi.BqqLayer(ok, p, p, p, p, p, p, None, 5, 0)
+    assert lib.bqq_forward_decode(baddt, p, 0, 1, 32, p, 0, 32, None, 0, None) == -6    # coefficient dtype
 
 
 @pytest.mark.parametrize('name', LAYER_CASES)

@@ -11,7 +11,10 @@ from tests.test_gpu_pack import _module_from_golden
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3        # contract
-TOL_FP32 = 2e-5   # what fp32 activations through the fp32-accumulating decode kernel should reach
+# what the decode kernel should reach with fp32 outputs: x is quantised to 16-bit block fixed
+# point per col patch (error <= 2^-16 of the patch maximum per element), everything else is exact
+# integer arithmetic or fp32
+TOL_FP32 = 1e-4
 
 
 def _run(bq, X):
@@ -104,7 +107,8 @@ def test_prefill_fp32_output_tolerance():
     xg = X.cuda()
     y = torch.empty(256, 256, dtype=torch.float32, device='cuda')
     ws = _workspace(xg.device, 'prefill', _cabi.lib.bqq_prefill_workspace_bytes(st.dims, 256))
-    rc = _cabi.lib.bqq_forward_prefill(st.layer, xg.data_ptr(), _cabi.BF16, 256, xg.stride(0), y.data_ptr(),
+    layer = bq._layer(st)
+    rc = _cabi.lib.bqq_forward_prefill(layer, xg.data_ptr(), _cabi.BF16, 256, xg.stride(0), y.data_ptr(),
                                        _cabi.F32, y.stride(0), ws.data_ptr(), ws.numel(),
                                        torch.cuda.current_stream().cuda_stream)
     assert rc == 0

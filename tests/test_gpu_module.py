@@ -59,7 +59,7 @@ def test_construct_without_init():
     bq.bias = None
     bq = bq.cuda()
     X = torch.randn(1, cw * gs, generator=g)
-    assert O.max_rel_err(_fwd(bq, X.cuda()).cpu().numpy(), oracle_forward_t(Y, Z, A, None, X)) < 2e-5
+    assert O.max_rel_err(_fwd(bq, X.cuda()).cpu().numpy(), oracle_forward_t(Y, Z, A, None, X)) < 1e-4
 
 
 def test_in_place_coefficient_update_is_seen():
@@ -75,7 +75,7 @@ def test_in_place_coefficient_update_is_seen():
     A2[0, ..., 3] += 0.5
     y1 = _fwd(bq, X.cuda())
     assert not torch.equal(y0, y1)
-    assert O.max_rel_err(y1.cpu().numpy(), oracle_forward_t(Y, Z, A2, None, X)) < 2e-5
+    assert O.max_rel_err(y1.cpu().numpy(), oracle_forward_t(Y, Z, A2, None, X)) < 1e-4
 
 
 def test_bfloat16_cast_and_device_moves():
@@ -107,13 +107,12 @@ def test_errors():
 
 
 def test_sharded_rows_equal_unsharded():
-    """Column-parallel shards (output-row patches) reproduce the full layer (fp32 summation
-    order may differ with the number of row patches per launch, nothing else)."""
+    """Column-parallel shards (output-row patches) reproduce the full layer bit for bit: the
+    decode kernel's work split never depends on the number of row patches."""
     from bqq_b200.bqq_modules import BinaryQuadratic, shard_rows
     Y, Z, A, bias, X = synth_layer(2, 8, 6, 32, 32, 32, 4, seed=8, bias=True)
     bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
     full = _fwd(bq, X.cuda())
     for world in (2, 4, 8):
         parts = [_fwd(shard_rows(bq, r, world), X.cuda()) for r in range(world)]
-        got = torch.cat(parts, dim=-1)
-        assert (got - full).abs().max().item() <= 1e-5 * full.abs().max().item()
+        assert torch.equal(torch.cat(parts, dim=-1), full)

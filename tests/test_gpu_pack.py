@@ -38,18 +38,6 @@ def test_planes_bit_exact(name):
     assert np.array_equal(Y2.cpu().numpy(), g['Y']) and np.array_equal(Z2.cpu().numpy(), g['Z'])
 
 
-@pytest.mark.parametrize('name', LAYER_CASES)
-def test_coefficient_records(name):
-    g = load_golden(name)
-    bq = _module_from_golden(g)
-    st = bq._ensure_packed()
-    want = O.pack_coefficients(g['a'], g['b'], g['c'], g['d']).reshape(-1)
-    got = st.coef.cpu().numpy()
-    assert np.array_equal(got[:-4], want)
-    m1 = (np.abs(g['a']) + np.abs(g['b']) + np.abs(g['c'])).max()
-    assert got[-4] == pytest.approx(m1, rel=1e-6) and got[-3] == pytest.approx(np.abs(g['d']).max(), rel=1e-6)
-
-
 @pytest.mark.parametrize('name', ['layer_0', 'layer_2', 'fused_s123', 'extend_3bit'])
 def test_reference_u8_checkpoint_repack(name):
     """Planes built from the reference's PackedBinaryQuadratic buffers equal planes built from bools."""
@@ -64,6 +52,7 @@ def test_reference_u8_checkpoint_repack(name):
         g['dims'][5], g['dims'][3], g['dims'][4]).cuda()
     st2 = pk._ensure_packed()
     assert torch.equal(st.zplanes, st2.zplanes) and torch.equal(st.yplanes, st2.yplanes)
+    assert torch.equal(st.ysum, st2.ysum) and torch.equal(st.zsum, st2.zsum)
     # our from_unpacked reproduces the reference's big-endian bytes
     pk2 = PackedBinaryQuadratic.from_unpacked(bq)
     assert np.array_equal(pk2.Y_packed.cpu().numpy(), g['Y_packed'])
