@@ -23,6 +23,7 @@ EXPORTS = [
     'bqq_decode_workspace_bytes', 'bqq_forward_decode',
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
+    'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc',
 ]
 
 
@@ -62,6 +63,8 @@ def _load():
         'bqq_forward_prefill': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_forward': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_reconstruct_weight': (i32, [lp, vp, i32, f32, vp]),
+        'bqq_noalloc_scratch_bytes': (sz, []),
+        'bqq_forward_decode_noalloc': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -41,6 +41,8 @@ const char* bqq_strerror(int rc) {
     case BQQ_ERR_CUDA: return "a CUDA call failed";
     case BQQ_ERR_TIMEOUT: return "a bounded device-side wait gave up";
     case BQQ_ERR_NO_DEVICE: return "no sm_100 GPU is current";
+    case BQQ_ERR_SCRATCH_LIMIT:
+      return "layer and batch need more scratch than the built-in array of the no-allocation entry point";
     default: return "unknown bqq error code";
   }
 }

@@ -42,6 +42,8 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   return pl;
 }
 
+size_t decode_counter_bytes() { return kCounterBytes; }
+
 size_t decode_workspace_bytes(const BqqDims* dims, int M) {
   Geom g(*dims);
   DecodePlan pl = make_decode_plan(g, M);

@@ -40,6 +40,7 @@ extern "C" {
 #define BQQ_ERR_CUDA         -7   /* a CUDA runtime / driver call failed           */
 #define BQQ_ERR_TIMEOUT      -8   /* a bounded device-side wait gave up            */
 #define BQQ_ERR_NO_DEVICE    -9   /* GPU is not an sm_100 device                   */
+#define BQQ_ERR_SCRATCH_LIMIT -10  /* needs more than the fixed built-in scratch     */
 
 /* element type codes for activations, outputs, coefficients and bias */
 #define BQQ_F32  0
@@ -51,6 +52,7 @@ extern "C" {
 #define BQQ_MAX_Q 128
 #define BQQ_MAX_R 64
 #define BQQ_DECODE_MAX_M 16     /* rows of X handled by the decode kernel */
+#define BQQ_NOALLOC_SCRATCH_BYTES (8u << 20)   /* built-in scratch of bqq_forward_decode_noalloc */
 
 /* bw bit layers, rw x cw patches of P x Q, rank r */
 typedef struct BqqDims {
@@ -166,6 +168,27 @@ size_t bqq_forward_workspace_bytes(const BqqDims* dims, int M);
 int bqq_forward(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
                 void* y, int y_dtype, int64_t ldy,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * bqq_forward_decode without a caller workspace (no counterpart in the reference,
+ * whose extension allocates through torch on every call).  It is for callers that
+ * cannot allocate device memory at the point of the call: operators hosted by a
+ * runtime that passes only input and output buffers, code inside a section where
+ * cudaMalloc or an allocating library call is not permitted, and start-up code
+ * that runs before an allocator exists.  The workspace is a fixed array of
+ * BQQ_NOALLOC_SCRATCH_BYTES (8 MiB) inside the library image, held by every GPU
+ * that loads the library until the process exits.  A layer / M whose
+ * bqq_decode_workspace_bytes exceeds that returns BQQ_ERR_SCRATCH_LIMIT and
+ * launches nothing.  The call performs no cudaMalloc, cudaFree or allocating
+ * library call.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current, so make that first call
+ * outside any stream capture.  All calls share the one array and it keeps the
+ * previous call's contents (the call clears the counters it relies on): calls
+ * that overlap on the GPU, on any streams, race with each other.
+ */
+size_t bqq_noalloc_scratch_bytes(void);
+int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
+                               void* y, int y_dtype, int64_t ldy, void* stream);
 
 /*
  * Dense weight W [rw*P, cw*Q] row-major in element type w_dtype: the value of
