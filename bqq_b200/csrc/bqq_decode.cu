@@ -34,7 +34,7 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   pl.nchunks = (g.JG + kDW * sgw - 1) / (kDW * sgw);
   pl.nparts = g.bw * pl.nchunks;
   const int PTv = kVariantPT[pl.variant], QTv = kVariantQT[pl.variant], RTv = kVariantRT[pl.variant];
-  pl.smem = (size_t)DecodeSmem(pl.NB, RTv, PTv).total;
+  pl.smem = (size_t)DecodeSmem(sgw, pl.NB, PTv, QTv, RTv).total;
   const size_t Mp = (size_t)pl.mtiles * pl.NB, cwp = (size_t)g.JG * kGroup;
   pl.xdig_bytes = align_up(Mp * cwp * 2 * QTv * 32, 256);
   pl.xmeta_bytes = 3 * align_up(Mp * cwp * 4, 256);     // scale, sum, l1
@@ -56,7 +56,8 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
   Geom g(L->dims);
   DecodePlan pl = make_decode_plan(g, M);
   if (pl.variant < 0) return BQQ_ERR_UNSUPPORTED;
-  if ((size_t)g.rw * pl.mtiles > (size_t)kMaxCounters) return BQQ_ERR_UNSUPPORTED;
+  if ((size_t)g.rw * pl.mtiles > (size_t)kMaxCounters - 1) return BQQ_ERR_UNSUPPORTED;   // last word: status
+  if ((size_t)g.bw * g.rw * g.cw >= (1ull << 31)) return BQQ_ERR_UNSUPPORTED;           // 32-bit coefficient offsets
   DecodeParams p;
   p.zp = reinterpret_cast<const uint4*>(L->zplanes);
   p.yp = reinterpret_cast<const uint4*>(L->yplanes);

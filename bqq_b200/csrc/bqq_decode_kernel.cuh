@@ -24,6 +24,7 @@
 // outputs.  CTA partial sums go to scratch; the last CTA of a row patch adds
 // them in a fixed order, adds bias and converts to the output type.
 #pragma once
+#include "bqq_async.cuh"
 #include "bqq_common.cuh"
 
 namespace bqq {
@@ -54,7 +55,7 @@ struct DecodeParams {
   const void* bias;
   float* partial;
   unsigned* counters;
-  const uint8_t* xdig;       // [Mp][cwp][2][QP] s8 digits of x (written by the preparation kernel)
+  const uint8_t* xdig;       // s8 digits of x, [Mp][JG][digit][QT][half][t][sub] words (preparation kernel)
   const float* xscale;       // [Mp][cwp] block scale of x
   const float* xsum;         // [Mp][cwp] sum_q x
   const float* xl1;          // [Mp][cwp] sum_q |x|
@@ -87,20 +88,30 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int sub) {
   return sub == 0 ? v.x : (sub == 1 ? v.y : (sub == 2 ? v.z : v.w));
 }
 
-// Shared-memory carve-up (bytes), shared by host plan and kernel.
+// Shared-memory carve-up (bytes), shared by host plan and kernel.  Everything a CTA reads from
+// global memory is staged here by bulk copies issued at kernel start: the plane words of its chunk
+// (one mbarrier per step of 4 super-groups), coefficients, x digits and x statistics.
 struct DecodeSmem {
-  int udig, red, total;
-  __host__ __device__ DecodeSmem(int NB, int RT, int PT) {
+  int bars, zs, ys, xd, coef, meta, udig, red, total;
+  __host__ __device__ DecodeSmem(int sgw, int NB, int PT, int QT, int RT) {
+    const int nsg = kDW * sgw;                        // super-groups per chunk
     int o = 0;
-    udig = o;   o += kDW * kGroup * NB * 4 * RT * 32; // u8 [warps][4 sub][NB][4 slots][RP]
-    red = o;    o += kDW * NB * PT * 32 * 4;          // f32 [warps][NB][PP]
+    bars = o;  o += 128;                              // up to 9 mbarriers (8 steps + misc)
+    zs = o;    o += nsg * RT * QT * 512;              // uint4 [nsg][RT][QT][32]
+    ys = o;    o += nsg * PT * RT * 512;              // uint4 [nsg][PT][RT][32]
+    xd = o;    o += NB * nsg * 2 * QT * 128;          // uint4 [NB][nsg][digit][QT][8]
+    coef = o;  o += 4 * nsg * 16;                     // float [a|b|c|d][nsg*4]
+    meta = o;  o += NB * 3 * nsg * 16;                // float [NB][scale|sum|l1][nsg*4]
+    udig = o;  o += kDW * kGroup * NB * 4 * RT * 32;  // u8 [warps][4 sub][NB][4 slots][RP]
+    red = o;   o += kDW * NB * PT * 32 * 4;           // f32 [warps][NB][PP]
     total = o;
   }
 };
+constexpr int kMaxSgw = 8;
 
 // ---- activation preparation ------------------------------------------------------------------
 // One pass over x [M, cw*Q]: per (row m, col patch j) the 16-bit block fixed point digits
-//   xdig [Mp][cwp][2][QP] (s8: x_int = lo + 256*hi, x ~ x_int * scale), QP = 32*QT,
+//   xdig (s8 digits: x_int = lo + 256*hi, x ~ x_int * scale), 2*32*QT bytes per pair,
 // and xscale / xsum / xl1 [Mp][cwp] = scale, sum_q x, sum_q |x|.  Rows m >= M and col patches
 // j >= cw (Mp, cwp: M and cw rounded up to the kernel's tiles) are written as zeros so that the
 // decode kernel needs no edge tests.  8 lanes share one (m, j) pair.
@@ -134,16 +145,23 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
   }
   if (!inside) return;
   const float inv = amax > 0.f ? 32512.f / amax : 0.f;
-  uint8_t* row = xdig + (size_t)pair * 2 * QP + sub8 * 4 * QT;
+  // digit layout [Mp][JG][digit][QT][half][t][sub] words (4 consecutive q each): the 4 col patches of a
+  // super-group are adjacent, so a lane of the decode kernel fetches its B-operand words of a whole
+  // super-group with one 128-bit load per (digit, half)
+  const int JG = cwp / kGroup;
+  uint32_t* words = reinterpret_cast<uint32_t*>(xdig);
 #pragma unroll
   for (int w4 = 0; w4 < QT; ++w4) {
     uint32_t D[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) D[e] = (uint32_t)(__float2int_rn(v[w4 * 4 + e] * inv) + 0x8080) ^ 0x8080u;
+    const int q4 = sub8 * QT + w4;                 // index of this group of 4 consecutive q
+    const int qt = q4 >> 3, half = (q4 >> 2) & 1, tt = q4 & 3;
+    const size_t base = ((size_t)m * JG + (j >> 2)) * 2;
     // x_int = lo + 256*hi with both digits signed bytes
-    *reinterpret_cast<uint32_t*>(row + w4 * 4) =
+    words[((((base + 0) * QT + qt) * 2 + half) * 4 + tt) * kGroup + (j & 3)] =
         __byte_perm(__byte_perm(D[0], D[1], 0x0040), __byte_perm(D[2], D[3], 0x0040), 0x5410);
-    *reinterpret_cast<uint32_t*>(row + QP + w4 * 4) =
+    words[((((base + 1) * QT + qt) * 2 + half) * 4 + tt) * kGroup + (j & 3)] =
         __byte_perm(__byte_perm(D[0], D[1], 0x0051), __byte_perm(D[2], D[3], 0x0051), 0x5410);
   }
   if (sub8 == 0) {
@@ -156,13 +174,18 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
 template <int PT, int QT, int RT, int NB>
 __global__ void __launch_bounds__(kDT)
 bqq_decode_kernel(const DecodeParams p) {
-  constexpr int QP = QT * 32;
   constexpr int RP = RT * 32;
   constexpr int PP = PT * 32;
   constexpr int NT2 = NB == 1 ? 1 : 2;              // n-tiles of the second contraction
-  constexpr bool kPrefetch = (RT * QT + PT * RT) <= 4;   // double-buffer the plane words in registers
-  extern __shared__ __align__(16) uint8_t sm[];
-  const DecodeSmem L(NB, RT, PT);
+  extern __shared__ __align__(128) uint8_t sm[];
+  const int nsg = kDW * p.sgw;                      // super-groups per chunk (smem row pitch)
+  const DecodeSmem L(p.sgw, NB, PT, QT, RT);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L.bars);      // [0..sgw) steps, [kMaxSgw] misc
+  const uint4* zs = reinterpret_cast<const uint4*>(sm + L.zs);
+  const uint4* ys = reinterpret_cast<const uint4*>(sm + L.ys);
+  const uint4* xd = reinterpret_cast<const uint4*>(sm + L.xd);
+  const float* scoef = reinterpret_cast<const float*>(sm + L.coef);
+  const float* smeta = reinterpret_cast<const float*>(sm + L.meta);
   uint8_t* udig = sm + L.udig;
   float* red = reinterpret_cast<float*>(sm + L.red);
 
@@ -177,55 +200,78 @@ bqq_decode_kernel(const DecodeParams p) {
   const int bit = bid % p.bw;
   const int i = bid / p.bw;
   const int m0 = blockIdx.y * NB;
-  const int jg0 = chunk * kDW * p.sgw;              // first col-patch group of the chunk
+  const int jg0 = chunk * nsg;                      // first col-patch group of the chunk
+  const int nvalid = min(nsg, p.JG - jg0);          // super-groups that exist in this chunk
+  const uint32_t crow = (uint32_t)(((size_t)bit * p.rw + i) * p.cw);   // coefficient row of (bit, i)
+  const uint32_t drow = (uint32_t)((size_t)i * p.cw);
 
-  // ---- plane loads of the warp's first super-group go out first ---------------------------
-  uint4 zw[RT][QT], yw[PT][RT];
-  uint4 zn[kPrefetch ? RT : 1][kPrefetch ? QT : 1], yn[kPrefetch ? PT : 1][kPrefetch ? RT : 1];
-  auto load_planes = [&](int jg, uint4 (&zd)[kPrefetch ? RT : 1][kPrefetch ? QT : 1],
-                         uint4 (&yd)[kPrefetch ? PT : 1][kPrefetch ? RT : 1], bool into_next) {
-    const size_t sg = (size_t)i * p.NS + (size_t)bit * p.JG + jg;
+  // ---- one thread issues every copy of the CTA; consumers wait on the mbarriers -----------------
+  if (tid == 0) {
+    for (int b = 0; b <= kMaxSgw; ++b) mbar_init(bars + b, 1);
+    mbar_init_fence();
+    const uint32_t n16 = (uint32_t)nvalid * 16u;                    // bytes of nvalid*4 floats
+    uint32_t misc = NB * (3 * n16 + (uint32_t)nvalid * 2 * QT * 128);
+    if (p.coef_vec) misc += 3 * n16 + (bit == 0 ? n16 : 0u);
+    mbar_expect_tx(bars + kMaxSgw, misc);
+    if (p.coef_vec) {
+      float* sc = const_cast<float*>(scoef);
+      bulk_load(sc, reinterpret_cast<const float*>(p.a) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      bulk_load(sc + nsg * 4, reinterpret_cast<const float*>(p.b) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      bulk_load(sc + nsg * 8, reinterpret_cast<const float*>(p.c) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      if (bit == 0)
+        bulk_load(sc + nsg * 12, reinterpret_cast<const float*>(p.d) + drow + jg0 * kGroup, n16, bars + kMaxSgw);
+    }
 #pragma unroll
-    for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-      for (int qt = 0; qt < QT; ++qt) {
-        const uint4 v = (rt < p.RTg && qt < p.QTg && jg < p.JG)
-                            ? load_plane_u4(p.zp + ((sg * p.RTg + rt) * p.QTg + qt) * 32 + lane)
-                            : make_uint4(0u, 0u, 0u, 0u);
-        if (kPrefetch && into_next) zd[kPrefetch ? rt : 0][kPrefetch ? qt : 0] = v; else zw[rt][qt] = v;
-      }
-#pragma unroll
-    for (int pt = 0; pt < PT; ++pt)
-#pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-        const uint4 v = (pt < p.PTg && rt < p.RTg && jg < p.JG)
-                            ? load_plane_u4(p.yp + ((sg * p.PTg + pt) * p.RTg + rt) * 32 + lane)
-                            : make_uint4(0u, 0u, 0u, 0u);
-        if (kPrefetch && into_next) yd[kPrefetch ? pt : 0][kPrefetch ? rt : 0] = v; else yw[pt][rt] = v;
-      }
-  };
-  load_planes(jg0 + warp, zn, yn, false);
+    for (int beta = 0; beta < NB; ++beta) {
+      const size_t row = (size_t)(m0 + beta) * p.cwp + (size_t)jg0 * kGroup;
+      float* sm_meta = const_cast<float*>(smeta) + beta * 3 * nsg * 4;
+      bulk_load(sm_meta, p.xscale + row, n16, bars + kMaxSgw);
+      bulk_load(sm_meta + nsg * 4, p.xsum + row, n16, bars + kMaxSgw);
+      bulk_load(sm_meta + nsg * 8, p.xl1 + row, n16, bars + kMaxSgw);
+      bulk_load(const_cast<uint4*>(xd) + (size_t)beta * nsg * 2 * QT * 8,
+                reinterpret_cast<const uint4*>(p.xdig) + ((size_t)(m0 + beta) * p.JG + jg0) * 2 * QT * 8,
+                (uint32_t)nvalid * 2 * QT * 128, bars + kMaxSgw);
+    }
+    const uint32_t zb = (uint32_t)p.RTg * p.QTg * 512, yb = (uint32_t)p.PTg * p.RTg * 512;   // bytes per super-group
+    const size_t sg0 = (size_t)i * p.NS + (size_t)bit * p.JG + jg0;
+    for (int it = 0; it < p.sgw; ++it) {
+      const int nv = min(kDW, nvalid - kDW * it);
+      if (nv <= 0) break;
+      mbar_expect_tx(bars + it, (uint32_t)nv * (zb + yb));
+      bulk_load(const_cast<uint4*>(zs) + (size_t)it * kDW * (zb / 16), p.zp + (sg0 + kDW * it) * (zb / 16),
+                (uint32_t)nv * zb, bars + it);
+      bulk_load(const_cast<uint4*>(ys) + (size_t)it * kDW * (yb / 16), p.yp + (sg0 + kDW * it) * (yb / 16),
+                (uint32_t)nv * yb, bars + it);
+    }
+  }
 
   // ---- zero the digit exchange buffer (slot 3 of every row must stay zero) --------------------
   constexpr int kUSub = NB * 4 * RP;                 // bytes of one col patch's u digits
   uint8_t* my_udig = udig + (size_t)warp * kGroup * kUSub;
   for (int e = lane; e < kGroup * kUSub / 4; e += 32) reinterpret_cast<uint32_t*>(my_udig)[e] = 0u;
+  __syncthreads();                                   // barriers are initialised for every waiter
+  bool ok = mbar_wait(bars + kMaxSgw, 0);
 
   // ---- fixed-point scale of u for this warp: bound |a| sum|x| + |b| |sum x| over its patch-bits
   const int my_beta = NB == 1 ? 0 : t;
   float ub = 0.f;
   {
     const int it = lane >> 2, sub = lane & 3;
-    const int jg = jg0 + warp + kDW * it;
-    const int j = jg * kGroup + sub;
-    if (it < p.sgw && jg < p.JG && j < p.cw) {
-      const size_t ci = ((size_t)bit * p.rw + i) * p.cw + j;
-      const float ca = fabsf(load_as_float(p.a, ci, p.coef_dtype));
-      const float cb = fabsf(load_as_float(p.b, ci, p.coef_dtype));
+    const int sgi = kDW * it + warp;                 // super-group index inside the chunk
+    const int j = (jg0 + sgi) * kGroup + sub;
+    if (it < p.sgw && sgi < nvalid && j < p.cw) {
+      float ca, cb;
+      if (p.coef_vec) {
+        ca = fabsf(scoef[sgi * 4 + sub]);
+        cb = fabsf(scoef[nsg * 4 + sgi * 4 + sub]);
+      } else {
+        ca = fabsf(load_as_float(p.a, crow + j, p.coef_dtype));
+        cb = fabsf(load_as_float(p.b, crow + j, p.coef_dtype));
+      }
 #pragma unroll
       for (int beta = 0; beta < NB; ++beta) {
-        const size_t xi = (size_t)(m0 + beta) * p.cwp + j;
-        ub = fmaxf(ub, fmaf(ca, p.xl1[xi], cb * fabsf(p.xsum[xi])));
+        const float* mrow = smeta + beta * 3 * nsg * 4;
+        ub = fmaxf(ub, fmaf(ca, mrow[nsg * 8 + sgi * 4 + sub], cb * fabsf(mrow[nsg * 4 + sgi * 4 + sub])));
       }
     }
 #pragma unroll
@@ -249,9 +295,8 @@ bqq_decode_kernel(const DecodeParams p) {
   const int f0 = e0 << 8, f1 = e1 << 8, f2 = e2 << 8, f3 = e3 << 8;
   // lane constants: where this lane's B-operand column (n = g) finds its x digits, where the
   // lane's row of X keeps scale and sum, where its u digits go and come from
-  const uint8_t* xlane = p.xdig + ((size_t)(m0 + (NB == 1 ? 0 : (g >> 1))) * p.cwp * 2 + (g & 1)) * QP + 4 * t;
-  const float* xsc_row = p.xscale + (size_t)(m0 + my_beta) * p.cwp;
-  const float* xs_row = p.xsum + (size_t)(m0 + my_beta) * p.cwp;
+  const uint4* xlane = xd + ((size_t)(NB == 1 ? 0 : (g >> 1)) * nsg * 2 + (g & 1)) * (QT * 8) + t;
+  const float* mrow = smeta + my_beta * 3 * nsg * 4;   // [scale | sum | l1] of this lane's row of X
   uint8_t* ust = my_udig + (NB == 1 ? g + 8 * t : t * 4 * RP + g);
   const uint8_t* uld[NT2];
 #pragma unroll
@@ -260,62 +305,65 @@ bqq_decode_kernel(const DecodeParams p) {
     const int slot = NB == 1 ? min(g, 3) : (g & 3);      // slot 3 stays zero
     uld[nt] = my_udig + (beta * 4 + slot) * RP + 4 * t;
   }
-  const float* pa = reinterpret_cast<const float*>(p.a);
-  const float* pb = reinterpret_cast<const float*>(p.b);
-  const float* pc = reinterpret_cast<const float*>(p.c);
-  const float* pd = reinterpret_cast<const float*>(p.d);
-  const uint32_t crow = (uint32_t)(((size_t)bit * p.rw + i) * p.cw);   // coefficient row of (bit, i)
-  const uint32_t drow = (uint32_t)((size_t)i * p.cw);
   constexpr float kMagic = 12582912.f;                // 1.5 * 2^23: float -> int by mantissa alignment
   constexpr uint32_t kUnbias = 0x808080u - 0x4B400000u;
 
   for (int it = 0; it < p.sgw; ++it) {
-    const int jg = jg0 + warp + kDW * it;
-    if (jg >= p.JG) break;
-    if (kPrefetch) {
-      if (it + 1 < p.sgw) load_planes(jg + kDW, zn, yn, true);
-    } else if (it > 0) {
-      load_planes(jg, zn, yn, false);
-    }
-    const uint32_t jb = (uint32_t)jg * kGroup;
+    const int sgi = kDW * it + warp;                  // super-group index inside the chunk
+    if (sgi >= nvalid) break;
+    ok = mbar_wait(bars + it, 0) && ok;
+    // plane words of this super-group
+    uint4 zw[RT][QT], yw[PT][RT];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+      for (int qt = 0; qt < QT; ++qt)
+        zw[rt][qt] = (rt < p.RTg && qt < p.QTg) ? zs[((size_t)(sgi * p.RTg + rt) * p.QTg + qt) * 32 + lane]
+                                                  : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int pt = 0; pt < PT; ++pt)
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt)
+        yw[pt][rt] = (pt < p.PTg && rt < p.RTg) ? ys[((size_t)(sgi * p.PTg + pt) * p.RTg + rt) * 32 + lane]
+                                                  : make_uint4(0u, 0u, 0u, 0u);
     // per super-group: coefficients, x scale / sum and the x digit registers of its 4 col patches
     float ca4[4], cb4[4], cc4[4], cd4[4];
     if (p.coef_vec) {
-      const float4 va = *reinterpret_cast<const float4*>(pa + crow + jb);
-      const float4 vb = *reinterpret_cast<const float4*>(pb + crow + jb);
-      const float4 vc = *reinterpret_cast<const float4*>(pc + crow + jb);
+      const float4 va = *reinterpret_cast<const float4*>(scoef + sgi * 4);
+      const float4 vb = *reinterpret_cast<const float4*>(scoef + nsg * 4 + sgi * 4);
+      const float4 vc = *reinterpret_cast<const float4*>(scoef + nsg * 8 + sgi * 4);
       ca4[0] = va.x; ca4[1] = va.y; ca4[2] = va.z; ca4[3] = va.w;
       cb4[0] = vb.x; cb4[1] = vb.y; cb4[2] = vb.z; cb4[3] = vb.w;
       cc4[0] = vc.x; cc4[1] = vc.y; cc4[2] = vc.z; cc4[3] = vc.w;
       if (bit == 0) {
-        const float4 vd = *reinterpret_cast<const float4*>(pd + drow + jb);
+        const float4 vd = *reinterpret_cast<const float4*>(scoef + nsg * 12 + sgi * 4);
         cd4[0] = vd.x; cd4[1] = vd.y; cd4[2] = vd.z; cd4[3] = vd.w;
       } else {
         cd4[0] = cd4[1] = cd4[2] = cd4[3] = 0.f;
       }
     } else {
+      const uint32_t jb = (uint32_t)(jg0 + sgi) * kGroup;
 #pragma unroll
       for (int sub = 0; sub < kGroup; ++sub) {
-        const bool ok = (int)(jb + sub) < p.cw;          // ragged last group: zero coefficients
-        ca4[sub] = ok ? load_as_float(p.a, crow + jb + sub, p.coef_dtype) : 0.f;
-        cb4[sub] = ok ? load_as_float(p.b, crow + jb + sub, p.coef_dtype) : 0.f;
-        cc4[sub] = ok ? load_as_float(p.c, crow + jb + sub, p.coef_dtype) : 0.f;
-        cd4[sub] = (ok && bit == 0) ? load_as_float(p.d, drow + jb + sub, p.coef_dtype) : 0.f;
+        const bool in = (int)(jb + sub) < p.cw;          // ragged last group: zero coefficients
+        ca4[sub] = in ? load_as_float(p.a, crow + jb + sub, p.coef_dtype) : 0.f;
+        cb4[sub] = in ? load_as_float(p.b, crow + jb + sub, p.coef_dtype) : 0.f;
+        cc4[sub] = in ? load_as_float(p.c, crow + jb + sub, p.coef_dtype) : 0.f;
+        cd4[sub] = (in && bit == 0) ? load_as_float(p.d, drow + jb + sub, p.coef_dtype) : 0.f;
       }
     }
-    const float4 xsc4 = *reinterpret_cast<const float4*>(xsc_row + jb);
-    const float4 xs4 = *reinterpret_cast<const float4*>(xs_row + jb);
+    const float4 xsc4 = *reinterpret_cast<const float4*>(mrow + sgi * 4);
+    const float4 xs4 = *reinterpret_cast<const float4*>(mrow + nsg * 4 + sgi * 4);
     const float xscv[4] = {xsc4.x, xsc4.y, xsc4.z, xsc4.w};
     const float xsv[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
     uint32_t bx0[kGroup][QT], bx1[kGroup][QT];
 #pragma unroll
-    for (int sub = 0; sub < kGroup; ++sub)
-#pragma unroll
-      for (int qt = 0; qt < QT; ++qt) {
-        const uint8_t* src = xlane + (jb + sub) * (2 * QP) + qt * 32;
-        bx0[sub][qt] = *reinterpret_cast<const uint32_t*>(src);
-        bx1[sub][qt] = *reinterpret_cast<const uint32_t*>(src + 16);
-      }
+    for (int qt = 0; qt < QT; ++qt) {
+      const uint4 h0 = xlane[(size_t)sgi * (2 * QT * 8) + qt * 8];
+      const uint4 h1 = xlane[(size_t)sgi * (2 * QT * 8) + qt * 8 + 4];
+      bx0[0][qt] = h0.x; bx0[1][qt] = h0.y; bx0[2][qt] = h0.z; bx0[3][qt] = h0.w;
+      bx1[0][qt] = h1.x; bx1[1][qt] = h1.y; bx1[2][qt] = h1.z; bx1[3][qt] = h1.w;
+    }
 
 #pragma unroll
     for (int sub = 0; sub < kGroup; ++sub) {
@@ -401,17 +449,9 @@ bqq_decode_kernel(const DecodeParams p) {
       }
     }
     __syncwarp();
-    if (kPrefetch) {
-#pragma unroll
-      for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-        for (int qt = 0; qt < QT; ++qt) zw[rt][qt] = zn[kPrefetch ? rt : 0][kPrefetch ? qt : 0];
-#pragma unroll
-      for (int pt = 0; pt < PT; ++pt)
-#pragma unroll
-        for (int rt = 0; rt < RT; ++rt) yw[pt][rt] = yn[kPrefetch ? pt : 0][kPrefetch ? rt : 0];
-    }
   }
+
+  if (!ok && lane == 0) atomicExch(p.counters + (kMaxCounters - 1), 1u);   // a bounded wait gave up
 
   // ---- warp epilogue: digits -> float, undo the 2^rr row scales, add c and d terms -----------
   // cacc holds the lane's share of c * sum_k t_k for row my_beta of X; dacc the d term.

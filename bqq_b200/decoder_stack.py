@@ -1,0 +1,162 @@
+"""Random-init Llama-style decoder stack whose Linear layers are BinaryQuadratic.
+
+This is the harness for the full-model decode configuration: 32 layers, hidden 4096,
+intermediate 14336, 32 query / 8 KV heads, vocabulary 128256, every q/k/v/o/gate/up/down
+projection replaced by a BinaryQuadratic layer (2 bit layers, P=Q=r=32), embeddings and
+lm_head kept dense because the reference's replacement skips names containing 'head'
+(lm/build_bqq_model.py:89-91) and the reference benchmark also skips 'embed'
+(lm/benchmark_inference.py:47-49).  It follows the recipe of the reference's only end-to-end
+decode loop (lm/benchmark_inference.py:24-85): random binary factors, greedy decode with a
+KV cache.
+
+Only the BinaryQuadratic layers are the product here; normalisation, rotary embedding,
+attention and the dense lm_head are plain torch ops (plumbing).  With world > 1 the layers are
+column-parallel (bqq_b200/sharded.py): q/k/v are sharded by heads so attention runs on local
+heads, gate/up share one sharding so SwiGLU is local, o_proj and down_proj are row-patch
+sharded; four all-gathers per layer, all without reductions.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .bqq_modules import BinaryQuadratic
+from .sharded import gather_columns
+
+
+@dataclass
+class StackConfig:
+    layers: int = 32
+    hidden: int = 4096
+    intermediate: int = 14336
+    heads: int = 32
+    kv_heads: int = 8
+    vocab: int = 128256
+    bit_width: int = 2
+    group: int = 32            # P = Q = r
+    max_seq: int = 1024
+    rope_theta: float = 500000.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+
+def random_bq(out_f: int, in_f: int, cfg: StackConfig, device, gen) -> BinaryQuadratic:
+    """Random BinaryQuadratic of the given shape, built on the device (bits Bernoulli(0.5),
+    coefficients N(0, 0.02)); same construction as make_random_bqq in the reference benchmark."""
+    gs, bw = cfg.group, cfg.bit_width
+    rw, cw = out_f // gs, in_f // gs
+    Y = torch.rand(bw, rw, cw, gs, gs, generator=gen, device=device) > 0.5
+    Z = torch.rand(bw, rw, cw, gs, gs, generator=gen, device=device) > 0.5
+    # coefficients scaled so activations keep a sane magnitude through 32 layers
+    A = torch.randn(bw, rw, cw, 4, generator=gen, device=device) * (0.02 / math.sqrt(in_f / 4096))
+    A[..., 1:] *= 0.05        # b, c, d act on sums of many entries
+    bq = BinaryQuadratic(Y, Z, A)
+    bq._ensure_packed()
+    # the bool factors are only needed for packing; keep a 1-row stub so memory stays at the packed size
+    return bq
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: StackConfig, device, gen, rank: int, world: int):
+        super().__init__()
+        self.cfg, self.rank, self.world = cfg, rank, world
+        hd = cfg.head_dim
+        self.local_heads = cfg.heads // world
+        self.local_kv = max(1, cfg.kv_heads // world)
+        if cfg.heads % world or (cfg.kv_heads % world and world % cfg.kv_heads):
+            raise ValueError('heads must divide evenly over the ranks')
+        h = cfg.hidden
+        # each rank builds only its own row-patch shard (a shard is a layer with fewer row patches)
+        self.q_proj = random_bq(self.local_heads * hd, h, cfg, device, gen)
+        self.k_proj = random_bq(self.local_kv * hd, h, cfg, device, gen)
+        self.v_proj = random_bq(self.local_kv * hd, h, cfg, device, gen)
+        self.o_proj = random_bq(h // world, h, cfg, device, gen)
+        self.gate_proj = random_bq(cfg.intermediate // world, h, cfg, device, gen)
+        self.up_proj = random_bq(cfg.intermediate // world, h, cfg, device, gen)
+        self.down_proj = random_bq(h // world, cfg.intermediate, cfg, device, gen)
+        self.norm1 = nn.Parameter(torch.ones(h, device=device, dtype=torch.bfloat16))
+        self.norm2 = nn.Parameter(torch.ones(h, device=device, dtype=torch.bfloat16))
+
+    def _gather(self, y):
+        return gather_columns(y) if self.world > 1 else y
+
+    def forward(self, x, k_cache, v_cache, pos: int, cos, sin):
+        """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim]; writes positions pos..pos+T."""
+        cfg = self.cfg
+        B, T, _ = x.shape
+        hd = cfg.head_dim
+        hx = F.rms_norm(x, (cfg.hidden,), self.norm1, 1e-5)
+        q = self.q_proj(hx).view(B, T, self.local_heads, hd).transpose(1, 2)
+        k = self.k_proj(hx).view(B, T, self.local_kv, hd).transpose(1, 2)
+        v = self.v_proj(hx).view(B, T, self.local_kv, hd).transpose(1, 2)
+        q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+        k_cache[:, :, pos:pos + T] = k
+        v_cache[:, :, pos:pos + T] = v
+        kk, vv = k_cache[:, :, :pos + T], v_cache[:, :, :pos + T]
+        att = F.scaled_dot_product_attention(q, kk, vv, is_causal=(T > 1), enable_gqa=True)
+        att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
+        x = x + self._gather(self.o_proj(att))                                              # gather 2
+        hx = F.rms_norm(x, (cfg.hidden,), self.norm2, 1e-5)
+        act = F.silu(self.gate_proj(hx)) * self.up_proj(hx)
+        act = self._gather(act)                                                             # gather 3
+        return x + self._gather(self.down_proj(act))                                        # gather 4
+
+
+def _rope(x, cos, sin):
+    x1, x2 = x[..., ::2], x[..., 1::2]
+    out = torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1)
+    return out.flatten(-2).to(x.dtype)
+
+
+class DecoderStack(nn.Module):
+    def __init__(self, cfg: StackConfig, device, seed: int = 0, rank: int = 0, world: int = 1):
+        super().__init__()
+        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        gen = torch.Generator(device=device).manual_seed(seed + 7919 * rank)
+        shared = torch.Generator(device=device).manual_seed(seed)            # identical on every rank
+        self.embed = (torch.randn(cfg.vocab, cfg.hidden, generator=shared, device=device) * 0.5).to(torch.bfloat16)
+        self.layers = nn.ModuleList(DecoderLayer(cfg, device, gen, rank, world) for _ in range(cfg.layers))
+        self.norm = torch.ones(cfg.hidden, device=device, dtype=torch.bfloat16)
+        # dense bf16 lm_head, vocabulary sharded over the ranks
+        self.lm_head = (torch.randn(cfg.vocab // world, cfg.hidden, generator=gen, device=device)
+                        * (1.0 / math.sqrt(cfg.hidden))).to(torch.bfloat16)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float() / cfg.head_dim))
+        ang = torch.arange(cfg.max_seq, device=device).float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+
+    def bqq_bytes_per_token(self) -> int:
+        """Packed bits + fp32 coefficients streamed per decoded token on this rank."""
+        from . import _cabi
+        total = 0
+        for layer in self.layers:
+            for m in layer.children():
+                if isinstance(m, BinaryQuadratic):
+                    total += _cabi.lib.bqq_algorithmic_bytes(m._dims())
+        return total
+
+    def new_cache(self, batch: int):
+        cfg = self.cfg
+        kv = max(1, cfg.kv_heads // self.world)
+        shape = (cfg.layers, 2, batch, kv, cfg.max_seq, cfg.head_dim)
+        return torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
+
+    @torch.no_grad()
+    def step(self, ids, cache, pos: int):
+        """ids [B, T] -> next-token ids [B] (greedy); writes cache positions pos..pos+T."""
+        x = self.embed[ids]
+        T = ids.shape[1]
+        cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
+        for li, layer in enumerate(self.layers):
+            x = layer(x, cache[li, 0], cache[li, 1], pos, cos, sin)
+        h = F.rms_norm(x[:, -1], (self.cfg.hidden,), self.norm, 1e-5)
+        logits = h @ self.lm_head.T                               # [B, vocab/world]
+        if self.world > 1:
+            logits = gather_columns(logits)
+        return logits.argmax(dim=-1)
