@@ -59,7 +59,6 @@ def random_bq(out_f: int, in_f: int, cfg: StackConfig, device, gen) -> BinaryQua
     A[..., 1:] *= 0.05        # b, c, d act on sums of many entries
     bq = BinaryQuadratic(Y, Z, A)
     bq._ensure_packed()
-    # the bool factors are only needed for packing; keep a 1-row stub so memory stays at the packed size
     return bq
 
 
@@ -87,8 +86,12 @@ class DecoderLayer(nn.Module):
     def _gather(self, y):
         return gather_columns(y) if self.world > 1 else y
 
-    def forward(self, x, k_cache, v_cache, pos: int, cos, sin):
-        """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim]; writes positions pos..pos+T."""
+    def forward(self, x, k_cache, v_cache, pos, cos, sin, mask=None):
+        """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim].
+
+        Prefill: `pos` is a Python int, positions pos..pos+T are written and attention is causal over
+        the prefix.  Decode (T = 1, graph-capturable): `pos` is a 1-element device tensor, the cache
+        row is written with index_copy_ and `mask` [1,1,1,max_seq] hides the unwritten tail."""
         cfg = self.cfg
         B, T, _ = x.shape
         hd = cfg.head_dim
@@ -97,10 +100,15 @@ class DecoderLayer(nn.Module):
         k = self.k_proj(hx).view(B, T, self.local_kv, hd).transpose(1, 2)
         v = self.v_proj(hx).view(B, T, self.local_kv, hd).transpose(1, 2)
         q, k = _rope(q, cos, sin), _rope(k, cos, sin)
-        k_cache[:, :, pos:pos + T] = k
-        v_cache[:, :, pos:pos + T] = v
-        kk, vv = k_cache[:, :, :pos + T], v_cache[:, :, :pos + T]
-        att = F.scaled_dot_product_attention(q, kk, vv, is_causal=(T > 1), enable_gqa=True)
+        if mask is None:
+            k_cache[:, :, pos:pos + T] = k
+            v_cache[:, :, pos:pos + T] = v
+            att = F.scaled_dot_product_attention(q, k_cache[:, :, :pos + T], v_cache[:, :, :pos + T],
+                                                 is_causal=(T > 1 and pos == 0), enable_gqa=True)
+        else:
+            k_cache.index_copy_(2, pos, k)
+            v_cache.index_copy_(2, pos, v)
+            att = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=mask, enable_gqa=True)
         att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
         x = x + self._gather(self.o_proj(att))                                              # gather 2
         hx = F.rms_norm(x, (cfg.hidden,), self.norm2, 1e-5)
@@ -147,16 +155,30 @@ class DecoderStack(nn.Module):
         shape = (cfg.layers, 2, batch, kv, cfg.max_seq, cfg.head_dim)
         return torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
 
-    @torch.no_grad()
-    def step(self, ids, cache, pos: int):
-        """ids [B, T] -> next-token ids [B] (greedy); writes cache positions pos..pos+T."""
-        x = self.embed[ids]
-        T = ids.shape[1]
-        cos, sin = self.cos[pos:pos + T], self.sin[pos:pos + T]
-        for li, layer in enumerate(self.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], pos, cos, sin)
-        h = F.rms_norm(x[:, -1], (self.cfg.hidden,), self.norm, 1e-5)
+    def _head(self, x_last):
+        h = F.rms_norm(x_last, (self.cfg.hidden,), self.norm, 1e-5)
         logits = h @ self.lm_head.T                               # [B, vocab/world]
         if self.world > 1:
             logits = gather_columns(logits)
         return logits.argmax(dim=-1)
+
+    @torch.no_grad()
+    def prefill(self, ids, cache):
+        """ids [B, T] prompt -> first generated token ids [B]; fills cache positions 0..T."""
+        x = self.embed[ids]
+        T = ids.shape[1]
+        cos, sin = self.cos[:T], self.sin[:T]
+        for li, layer in enumerate(self.layers):
+            x = layer(x, cache[li, 0], cache[li, 1], 0, cos, sin)
+        return self._head(x[:, -1])
+
+    @torch.no_grad()
+    def decode_step(self, ids, cache, pos):
+        """One greedy decode step with static shapes (CUDA-graph capturable).
+        ids [B] int64, pos 1-element int64 device tensor; returns next ids [B]."""
+        x = self.embed[ids].unsqueeze(1)
+        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+        mask = (torch.arange(self.cfg.max_seq, device=self.device) <= pos).view(1, 1, 1, -1)
+        for li, layer in enumerate(self.layers):
+            x = layer(x, cache[li, 0], cache[li, 1], pos, cos, sin, mask)
+        return self._head(x[:, -1])
