@@ -97,9 +97,18 @@ def main():
             'decode_ms_per_step': best_decode / steps,
             'prefill_ms': best_prefill, 'prefill_tokens_per_s': args.batch * args.prompt / (best_prefill * 1e-3),
             'bqq_bytes_per_token_per_gpu': model.bqq_bytes_per_token(),
-            'lm_head': 'dense bf16, included', 'data': 'synthetic (random init, random prompt ids)'}))
+            'lm_head': 'dense bf16, included', 'data': 'synthetic (random init, random prompt ids)'}),
+            flush=True)
+    graph.reset()
+    torch.cuda.synchronize()
     if world > 1:
+        import threading
+        timer = threading.Timer(30.0, lambda: os._exit(0))     # teardown must never hang the job
+        timer.daemon = True
+        timer.start()
+        dist.barrier()
         dist.destroy_process_group()
+        timer.cancel()
 
 
 if __name__ == '__main__':
