@@ -121,6 +121,9 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
                  uint8_t* __restrict__ xdig, float* __restrict__ xscale, float* __restrict__ xsum,
                  float* __restrict__ xl1) {
   constexpr int QP = QT * 32;
+  // the decode kernel of this layer may start now: it first streams its weight planes and only
+  // then waits (griddepcontrol.wait) for this grid to finish
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int sub8 = threadIdx.x & 7;
   const int pairs = Mp * cwp;
   const int pair = (blockIdx.x * 128 + threadIdx.x) >> 3;
@@ -213,25 +216,7 @@ bqq_decode_kernel(const DecodeParams p) {
     uint32_t misc = NB * (3 * n16 + (uint32_t)nvalid * 2 * QT * 128);
     if (p.coef_vec) misc += 3 * n16 + (bit == 0 ? n16 : 0u);
     mbar_expect_tx(bars + kMaxSgw, misc);
-    if (p.coef_vec) {
-      float* sc = const_cast<float*>(scoef);
-      bulk_load(sc, reinterpret_cast<const float*>(p.a) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
-      bulk_load(sc + nsg * 4, reinterpret_cast<const float*>(p.b) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
-      bulk_load(sc + nsg * 8, reinterpret_cast<const float*>(p.c) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
-      if (bit == 0)
-        bulk_load(sc + nsg * 12, reinterpret_cast<const float*>(p.d) + drow + jg0 * kGroup, n16, bars + kMaxSgw);
-    }
-#pragma unroll
-    for (int beta = 0; beta < NB; ++beta) {
-      const size_t row = (size_t)(m0 + beta) * p.cwp + (size_t)jg0 * kGroup;
-      float* sm_meta = const_cast<float*>(smeta) + beta * 3 * nsg * 4;
-      bulk_load(sm_meta, p.xscale + row, n16, bars + kMaxSgw);
-      bulk_load(sm_meta + nsg * 4, p.xsum + row, n16, bars + kMaxSgw);
-      bulk_load(sm_meta + nsg * 8, p.xl1 + row, n16, bars + kMaxSgw);
-      bulk_load(const_cast<uint4*>(xd) + (size_t)beta * nsg * 2 * QT * 8,
-                reinterpret_cast<const uint4*>(p.xdig) + ((size_t)(m0 + beta) * p.JG + jg0) * 2 * QT * 8,
-                (uint32_t)nvalid * 2 * QT * 128, bars + kMaxSgw);
-    }
+    // weights first: they do not depend on the activation preparation kernel
     const uint32_t zb = (uint32_t)p.RTg * p.QTg * 512, yb = (uint32_t)p.PTg * p.RTg * 512;   // bytes per super-group
     const size_t sg0 = (size_t)i * p.NS + (size_t)bit * p.JG + jg0;
     for (int it = 0; it < p.sgw; ++it) {
@@ -242,6 +227,28 @@ bqq_decode_kernel(const DecodeParams p) {
                 (uint32_t)nv * zb, bars + it);
       bulk_load(const_cast<uint4*>(ys) + (size_t)it * kDW * (yb / 16), p.yp + (sg0 + kDW * it) * (yb / 16),
                 (uint32_t)nv * yb, bars + it);
+    }
+    if (p.coef_vec) {
+      float* sc = const_cast<float*>(scoef);
+      bulk_load(sc, reinterpret_cast<const float*>(p.a) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      bulk_load(sc + nsg * 4, reinterpret_cast<const float*>(p.b) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      bulk_load(sc + nsg * 8, reinterpret_cast<const float*>(p.c) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      if (bit == 0)
+        bulk_load(sc + nsg * 12, reinterpret_cast<const float*>(p.d) + drow + jg0 * kGroup, n16, bars + kMaxSgw);
+    }
+    // the x digits and statistics come from the preparation kernel launched just before this one
+    // (programmatic dependent launch): wait for it to complete before copying its output
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int beta = 0; beta < NB; ++beta) {
+      const size_t row = (size_t)(m0 + beta) * p.cwp + (size_t)jg0 * kGroup;
+      float* sm_meta = const_cast<float*>(smeta) + beta * 3 * nsg * 4;
+      bulk_load(sm_meta, p.xscale + row, n16, bars + kMaxSgw);
+      bulk_load(sm_meta + nsg * 4, p.xsum + row, n16, bars + kMaxSgw);
+      bulk_load(sm_meta + nsg * 8, p.xl1 + row, n16, bars + kMaxSgw);
+      bulk_load(const_cast<uint4*>(xd) + (size_t)beta * nsg * 2 * QT * 8,
+                reinterpret_cast<const uint4*>(p.xdig) + ((size_t)(m0 + beta) * p.JG + jg0) * 2 * QT * 8,
+                (uint32_t)nvalid * 2 * QT * 128, bars + kMaxSgw);
     }
   }
 
@@ -548,8 +555,19 @@ static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cu
   bqq_xprep_kernel<QT><<<(pairs * 8 + 127) / 128, 128, 0, st>>>(
       p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, const_cast<uint8_t*>(p.xdig),
       const_cast<float*>(p.xscale), const_cast<float*>(p.xsum), const_cast<float*>(p.xl1));
-  dim3 grid(p.rw * p.bw * p.nchunks, pl.mtiles);
-  kern<<<grid, kDT, pl.smem, st>>>(p);
+  // decode kernel: programmatic dependent launch after the preparation kernel, so that its weight
+  // copies overlap the preparation; the kernel itself waits before it touches the prepared x
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.rw * p.bw * p.nchunks, pl.mtiles);
+  cfg.blockDim = dim3(kDT);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
 }
 
