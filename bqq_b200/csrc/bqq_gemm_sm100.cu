@@ -73,6 +73,7 @@ struct GemmParams {
   const void* bias;
   const float* bound_parts;  // device {max(|a|+|b|+|c|), max|d|} when W was scaled (fp16), else NULL
   float bound_mult;          // bw * r
+  const float* row_unscale;  // optional per-row factor of y (activation rows were scaled on staging)
   unsigned* status;          // device word, set nonzero when a wait timed out
   int64_t ldy;
   int y_dtype, bias_dtype;
@@ -178,8 +179,10 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
     if (warp == 2 && lane == 0) BQQ_MARK(7, ok ? 1u : 2u);   // accumulator barrier passed
     tc_fence_after();
     if (ok) {
-      const float inv_scale = p.bound_parts ? 1.f / w_scale_from_bound(p.bound_parts, p.bound_mult) : 1.f;
+      const float w_unscale = p.bound_parts ? 1.f / w_scale_from_bound(p.bound_parts, p.bound_mult) : 1.f;
       const int m = m0 + quarter * 32 + lane;
+      const float row_f = (p.row_unscale && m < p.M) ? p.row_unscale[m] : 1.f;
+      const float inv_scale = w_unscale * row_f;
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
@@ -256,6 +259,29 @@ __global__ void stage_x_kernel(const void* __restrict__ x, int x_dtype, int64_t 
   }
 }
 
+// bf16 rows -> fp16 rows scaled by a per-row power of two (max |x| of the row maps to at most 2^14,
+// so nothing overflows and every bf16 value in range converts exactly); row_unscale[m] = 1 / scale.
+// One warp per row.
+__global__ void stage_x_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int M, int K,
+                                           __half* __restrict__ out, float* __restrict__ row_unscale) {
+  const int lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= M) return;
+  const __nv_bfloat16* row = x + (size_t)m * ldx;
+  float amax = 0.f;
+  for (int k = lane; k < K; k += 32) amax = fmaxf(amax, fabsf(__bfloat162float(row[k])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  float scale = 1.f;
+  if (amax > 0.f && isfinite(amax)) {
+    int e;
+    frexpf(amax, &e);                        // amax = f * 2^e, f in [0.5, 1)
+    scale = exp2f((float)max(-100, min(100, 14 - e)));
+  }
+  for (int k = lane; k < K; k += 32) out[(size_t)m * K + k] = __float2half_rn(__bfloat162float(row[k]) * scale);
+  if (lane == 0) row_unscale[m] = 1.f / scale;
+}
+
 // ---- host side -----------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -330,8 +356,9 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
 
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return BQQ_ERR_CUDA;
 
-  // 1. dense W into scratch, in the activations' 16-bit format
-  const bool f16 = x_dtype == BQQ_F16;
+  // 1. dense W into scratch.  fp16 and bf16 activations use one fp16 W scaled by a power of two
+  //    (bf16 rows are re-staged as scaled fp16, exact); fp32 activations use the bf16 hi + lo pair.
+  const bool f16 = x_dtype != BQQ_F32;
   int rc;
   if (f16) {
     rc = coef_bound_launch(L, bound_parts, st);
@@ -342,11 +369,21 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   }
   if (rc) return rc;
 
-  // 2. x: used in place when it is a 16-bit tensor with TMA-compatible pitch, else staged
-  const bool direct = x_dtype != BQQ_F32 && (ldx % 8) == 0 && ((uintptr_t)x & 15) == 0;
+  // 2. x: fp16 is used in place when its pitch suits TMA; everything else is staged
+  const bool direct = x_dtype == BQQ_F16 && (ldx % 8) == 0 && ((uintptr_t)x & 15) == 0;
   const void* a_ptr = x;
   int64_t a_ld = ldx;
-  if (!direct) {
+  const float* row_unscale = nullptr;
+  if (x_dtype == BQQ_BF16) {
+    float* unscale = reinterpret_cast<float*>(xlo);          // the lo region is free on this path
+    stage_x_bf16_to_f16_kernel<<<(M + 7) / 8, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx, M, K,
+                                                           reinterpret_cast<__half*>(xhi), unscale);
+    rc = launch_status();
+    if (rc) return rc;
+    a_ptr = xhi;
+    a_ld = K;
+    row_unscale = unscale;
+  } else if (!direct) {
     size_t n = (size_t)M * K;
     int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
     stage_x_kernel<<<blocks, 256, 0, st>>>(x, x_dtype, ldx, M, K, K, xhi, xlo);
@@ -370,14 +407,13 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   GemmParams p;
   p.y = y; p.bias = L->bias; p.bound_parts = f16 ? bound_parts : nullptr; p.bound_mult = (float)(g.bw * g.r);
   p.status = status;
+  p.row_unscale = row_unscale;
   p.ldy = ldy; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
   p.M = M; p.N = N; p.K = K;
   p.dbg = g_gemm_dbg;
   for (int i = 0; i < 3; ++i) { p.a_sel[i] = 0; p.b_row[i] = 0; }
   if (f16) {
     p.passes = 1;
-  } else if (!split_x) {
-    p.passes = 2; p.b_row[1] = N;                       // x*Whi + x*Wlo
   } else {
     p.passes = 3; p.b_row[1] = N; p.a_sel[2] = 1;       // xhi*Whi + xhi*Wlo + xlo*Whi
   }

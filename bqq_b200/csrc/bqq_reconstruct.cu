@@ -4,8 +4,10 @@
 // i.e. BinaryQuadratic.get_weight (neural_network_compression/src/bqq_modules.py:48-55),
 // with the AND+popcount idea of reconstruct_W_kernel (src/bqq_cuda.cu:198-246).
 // A warp owns one 32x32 block of one patch: lane l first gathers row l of Y and
-// column l of Z (bits over the rank) out of the fragment-ordered plane words, then
-// the block is produced row by row so every store is a contiguous 32-element run.
+// column l of Z (bits over the rank) out of the fragment-ordered plane words with
+// nibble/byte multiply tricks, then the block is produced row by row (row words
+// broadcast by shuffle, accumulators in registers) so every store is a contiguous
+// 32-element run.
 #include "bqq_common.cuh"
 
 namespace bqq {
@@ -25,82 +27,92 @@ struct ReconParams {
   long long total_tasks;       // rw * cw * PT * QT
 };
 
+// Spread the 4 low bits of n to the least significant bits of 4 bytes.
+__device__ __forceinline__ uint32_t nibble_to_bytes(uint32_t n) { return (n * 0x00204081u) & 0x01010101u; }
+// Collect the least significant bits of 4 bytes into a nibble (byte e -> bit e).
+__device__ __forceinline__ uint32_t bytes_to_nibble(uint32_t y) { return ((y & 0x01010101u) * 0x01020408u) >> 24; }
+
+template <int RT>
 __global__ void __launch_bounds__(kReconWarps * 32)
 bqq_reconstruct_kernel(const ReconParams p) {
-  extern __shared__ uint32_t rsm[];          // [warps][2][bw][RT][32]: row words of Y, column words of Z
   const Geom& g = p.g;
   const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  uint32_t* yrow = rsm + (size_t)warp * 2 * g.bw * g.RT * 32;
-  uint32_t* zcol = yrow + (size_t)g.bw * g.RT * 32;
   const float scale = p.bound_parts ? p.scale * w_scale_from_bound(p.bound_parts, (float)(g.bw * g.r)) : p.scale;
   const size_t ldw = (size_t)g.cw * g.Q;
+  // this lane as a row of Y (p = 32pt + lane = 32pt + gp + 8rp) and as a column of Z
+  // (q = 32qt + lane = 32qt + 16qh + 4tq + eq)
+  const int gp = lane & 7, rp = lane >> 3;
+  const int qh = (lane >> 4) & 1, tq = (lane >> 2) & 3, eq = lane & 3;
+  const int zbase = 8 * eq + 4 * qh;
 
-  for (long long task = (long long)blockIdx.x * kReconWarps + warp; task < p.total_tasks;
+  for (long long task = (long long)blockIdx.x * kReconWarps + (threadIdx.x >> 5); task < p.total_tasks;
        task += (long long)gridDim.x * kReconWarps) {
     long long u = task;
     const int qt = (int)(u % g.QT); u /= g.QT;
     const int pt = (int)(u % g.PT); u /= g.PT;
     const int j = (int)(u % g.cw);
     const int i = (int)(u / g.cw);
-    const int pl = 32 * pt + lane;           // this lane's row of Y
-    const int ql = 32 * qt + lane;           // this lane's column of Z
+    const int sub = j % kGroup;
 
+    float acc[32];
+#pragma unroll
+    for (int pp = 0; pp < 32; ++pp) acc[pp] = 0.f;
     float colterm = load_as_float(p.d, (size_t)i * g.cw + j, p.coef_dtype);   // d + sum_b c_b popc(Zcol_b)
     float rowterm = 0.f;                                                      // sum_b b_b popc(Yrow_b), lane = row
     for (int b = 0; b < g.bw; ++b) {
       const size_t ci = ((size_t)b * g.rw + i) * g.cw + j;
+      const float ca = load_as_float(p.a, ci, p.coef_dtype);
       const float cb = load_as_float(p.b, ci, p.coef_dtype);
       const float cc = load_as_float(p.c, ci, p.coef_dtype);
+      const size_t sg = (size_t)i * g.NS + (size_t)b * g.JG + j / kGroup;
+      uint32_t yr[RT], zc[RT];
       int ys = 0, zs = 0;
-      for (int rt = 0; rt < g.RT; ++rt) {
-        uint32_t yr = 0, zc = 0;
-        // row pl of Y: ranks 32rt + 16kh + 4t + e live in the words of lanes 4*(pl&7) + t
-        for (int t = 0; t < 4; ++t) {
-          int bit;
-          const uint32_t w = p.yp[g.y_word(b, i, j, pl, 32 * rt + 4 * t, &bit)];
-          const int rr = (pl >> 3) & 3;
 #pragma unroll
-          for (int kh = 0; kh < 2; ++kh)
+      for (int rt = 0; rt < RT; ++rt) {
+        yr[rt] = 0u;
+        zc[rt] = 0u;
+        if (rt < g.RT) {
+          // row of Y: ranks 16kh + 4t + e sit in the words of lanes 4*gp + t at bits 8e + 4kh + rp
+          const uint32_t* yb = p.yp + (((sg * g.PT + pt) * g.RT + rt) * 32) * kGroup + sub;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) yr |= ((w >> (8 * e + 4 * kh + rr)) & 1u) << (16 * kh + 4 * t + e);
+          for (int t = 0; t < 4; ++t) {
+            const uint32_t w = yb[(4 * gp + t) * kGroup] >> rp;
+            yr[rt] |= bytes_to_nibble(w) << (4 * t);
+            yr[rt] |= bytes_to_nibble(w >> 4) << (16 + 4 * t);
+          }
+          // column of Z: ranks gg + 8rr sit in the words of lanes 4*gg + tq at bits 8eq + 4qh + rr
+          const uint32_t* zb = p.zp + (((sg * g.RT + rt) * g.QT + qt) * 32) * kGroup + sub;
+#pragma unroll
+          for (int gg = 0; gg < 8; ++gg) {
+            const uint32_t w = zb[(4 * gg + tq) * kGroup] >> zbase;
+            zc[rt] |= nibble_to_bytes(w & 0xFu) << gg;
+          }
+          ys += __popc(yr[rt]);
+          zs += __popc(zc[rt]);
         }
-        // column ql of Z: ranks 32rt + gg + 8rr live in the words of lanes 4*gg + t(ql)
-        for (int gg = 0; gg < 8; ++gg) {
-          int bit;
-          const uint32_t w = p.zp[g.z_word(b, i, j, 32 * rt + gg, ql, &bit)];
-          const int base = bit & ~3;          // 8e + 4qh
-#pragma unroll
-          for (int rr = 0; rr < 4; ++rr) zc |= ((w >> (base + rr)) & 1u) << (gg + 8 * rr);
-        }
-        yrow[(b * g.RT + rt) * 32 + lane] = yr;
-        zcol[(b * g.RT + rt) * 32 + lane] = zc;
-        ys += __popc(yr);
-        zs += __popc(zc);
       }
       rowterm = fmaf(cb, (float)ys, rowterm);
       colterm = fmaf(cc, (float)zs, colterm);
-    }
-    __syncwarp();
-
-    const int prow_max = min(32, g.P - 32 * pt);
-    for (int pp = 0; pp < prow_max; ++pp) {
-      float acc = colterm + __shfl_sync(0xffffffffu, rowterm, pp);
-      for (int b = 0; b < g.bw; ++b) {
-        const float ca = load_as_float(p.a, ((size_t)b * g.rw + i) * g.cw + j, p.coef_dtype);
+#pragma unroll
+      for (int pp = 0; pp < 32; ++pp) {
         int core = 0;
-        for (int rt = 0; rt < g.RT; ++rt)
-          core += __popc(yrow[(b * g.RT + rt) * 32 + pp] & zcol[(b * g.RT + rt) * 32 + lane]);
-        acc = fmaf(ca, (float)core, acc);
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) core += __popc(__shfl_sync(0xffffffffu, yr[rt], pp) & zc[rt]);
+        acc[pp] = fmaf(ca, (float)core, acc[pp]);
       }
-      if (ql < g.Q) {
+    }
+    const int prow_max = min(32, g.P - 32 * pt);
+    const int ql = 32 * qt + lane;
+#pragma unroll
+    for (int pp = 0; pp < 32; ++pp) {
+      const float rterm = __shfl_sync(0xffffffffu, rowterm, pp);
+      if (pp < prow_max && ql < g.Q) {
         const size_t at = (size_t)(i * g.P + 32 * pt + pp) * ldw + (size_t)j * g.Q + ql;
-        const float w = acc * scale;
+        const float w = (acc[pp] + colterm + rterm) * scale;
         store_from_float(p.W, at, p.w_dtype, w);
         if (p.W_lo) store_from_float(p.W_lo, at, p.w_dtype, w - round_to(w, p.w_dtype));
       }
     }
-    __syncwarp();
   }
 }
 
@@ -112,11 +124,10 @@ int reconstruct_launch(const BqqLayer* L, void* W, void* W_lo, int w_dtype, floa
   p.a = L->a; p.b = L->b; p.c = L->c; p.d = L->d; p.coef_dtype = L->coef_dtype;
   p.W = W; p.W_lo = W_lo; p.scale = scale; p.bound_parts = bound_parts; p.w_dtype = w_dtype;
   p.total_tasks = (long long)p.g.rw * p.g.cw * p.g.PT * p.g.QT;
-  const size_t smem = (size_t)kReconWarps * 2 * p.g.bw * p.g.RT * 32 * sizeof(uint32_t);
-  if (smem > 48 * 1024) return BQQ_ERR_UNSUPPORTED;
   long long blocks = (p.total_tasks + kReconWarps - 1) / kReconWarps;
-  if (blocks > 148LL * 16) blocks = 148LL * 16;
-  bqq_reconstruct_kernel<<<(int)blocks, kReconWarps * 32, smem, st>>>(p);
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (p.g.RT == 1) bqq_reconstruct_kernel<1><<<(int)blocks, kReconWarps * 32, 0, st>>>(p);
+  else bqq_reconstruct_kernel<2><<<(int)blocks, kReconWarps * 32, 0, st>>>(p);
   return launch_status();
 }
 
