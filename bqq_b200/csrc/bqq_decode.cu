@@ -1,5 +1,7 @@
 // Host side of the decode forward: launch plan and dispatch to the kernel variants
 // (algorithm and kernel in bqq_decode_kernel.cuh).
+#include <stdlib.h>
+
 #include "bqq_decode_kernel.cuh"
 
 namespace bqq {
@@ -14,9 +16,7 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 static const int kVariantPT[4] = {1, 2, 2, 4};
 static const int kVariantQT[4] = {1, 2, 2, 4};
 static const int kVariantRT[4] = {1, 1, 2, 2};
-static const int kVariantMaxSgw[4] = {8, 4, 2, 1};
-
-
+static const int kVariantMaxSgw[4] = {32, 16, 8, 4};
 
 // The plan depends on the patch geometry, the number of col patches and M only
 // (never on the number of row patches), so row shards reduce in the same order.
@@ -29,6 +29,7 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   pl.NB = M <= 1 ? 1 : 4;
   pl.mtiles = (M + pl.NB - 1) / pl.NB;
   int sgw = g.JG <= 16 ? 1 : (g.JG <= 48 ? 2 : (g.JG <= 96 ? 4 : 8));
+  if (const char* e = getenv("BQQ_DECODE_SGW")) sgw = atoi(e);
   if (sgw > kVariantMaxSgw[pl.variant]) sgw = kVariantMaxSgw[pl.variant];
   pl.sgw = sgw;
   pl.nchunks = (g.JG + kDW * sgw - 1) / (kDW * sgw);

@@ -19,16 +19,23 @@
 // errors are the two roundings (about 2^-16 of the patch maximum of |x|).
 //
 // Work split: CTA = (row patch i, bit layer b, chunk of col-patch groups, M tile);
-// warp w owns super-groups w, w+4, ... of the chunk.  The split never depends on
-// the number of row patches, so a row shard of a layer produces bit-identical
-// outputs.  CTA partial sums go to scratch; the last CTA of a row patch adds
-// them in a fixed order, adds bias and converts to the output type.
+// warp w owns a contiguous run of super-groups of the chunk and streams its plane
+// words and x digits through a private ring of shared-memory slots filled by 16-byte
+// asynchronous copies (cp.async groups), so warps never wait for one another in the
+// main loop; coefficients and x statistics of the chunk arrive by bulk copies on one
+// mbarrier.  The split never depends on the number of row patches, so a row shard of a
+// layer produces bit-identical outputs.  CTA partial sums go to scratch; the last
+// CTA of a row patch adds them in a fixed order, adds bias and converts to the
+// output type.
 #pragma once
 #include "bqq_async.cuh"
 #include "bqq_common.cuh"
 
 namespace bqq {
 
+#ifndef BQQ_DECODE_MINB
+#define BQQ_DECODE_MINB 6
+#endif
 constexpr int kDW = 4;                   // warps per CTA
 constexpr int kDT = kDW * 32;
 constexpr int kMaxCounters = 65536;      // fixed-size counter region at the start of the workspace
@@ -55,7 +62,7 @@ struct DecodeParams {
   const void* bias;
   float* partial;
   unsigned* counters;
-  const uint8_t* xdig;       // s8 digits of x, [Mp][JG][digit][QT][half][t][sub] words (preparation kernel)
+  const uint8_t* xdig;       // s8 digits of x, [Mp/NB][JG][NB][digit][QT][half][t][sub] words (preparation kernel)
   const float* xscale;       // [Mp][cwp] block scale of x
   const float* xsum;         // [Mp][cwp] sum_q x
   const float* xl1;          // [Mp][cwp] sum_q |x|
@@ -84,22 +91,35 @@ __device__ __forceinline__ void mma_u8s8_first(int (&c)[4], uint32_t a0, uint32_
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// unsigned x unsigned (second contraction: the u digits are unsigned bytes)
+__device__ __forceinline__ void mma_u8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ uint32_t pick(const uint4& v, int sub) {
   return sub == 0 ? v.x : (sub == 1 ? v.y : (sub == 2 ? v.z : v.w));
 }
 
-// Shared-memory carve-up (bytes), shared by host plan and kernel.  Everything a CTA reads from
-// global memory is staged here by bulk copies issued at kernel start: the plane words of its chunk
-// (one mbarrier per step of 4 super-groups), coefficients, x digits and x statistics.
+constexpr int kMaxSgw = 64;              // upper bound of super-groups per warp (resident coefficients: 64 B each)
+
+// Shared-memory carve-up (bytes), shared by host plan and kernel.  Per warp a ring of `stages`
+// slots, each holding one super-group: its Z words, Y words and the x digits of the CTA's rows.
+// Resident for the whole chunk: coefficients and x statistics (one mbarrier).
 struct DecodeSmem {
-  int bars, zs, ys, xd, coef, meta, udig, red, total;
-  __host__ __device__ DecodeSmem(int sgw, int NB, int PT, int QT, int RT) {
+  int bars, ring, slot, stages, yoff, xoff, coef, meta, udig, red, total;
+  __host__ __device__ constexpr DecodeSmem(int sgw, int NB, int PT, int QT, int RT)
+      : bars(0), ring(0), slot(0), stages(0), yoff(0), xoff(0), coef(0), meta(0), udig(0), red(0), total(0) {
     const int nsg = kDW * sgw;                        // super-groups per chunk
     int o = 0;
-    bars = o;  o += 128;                              // up to 9 mbarriers (8 steps + misc)
-    zs = o;    o += nsg * RT * QT * 512;              // uint4 [nsg][RT][QT][32]
-    ys = o;    o += nsg * PT * RT * 512;              // uint4 [nsg][PT][RT][32]
-    xd = o;    o += NB * nsg * 2 * QT * 128;          // uint4 [NB][nsg][digit][QT][8]
+    bars = o;  o += 128;                              // one mbarrier
+    yoff = RT * QT * 512;                             // slot: uint4 Z[RT][QT][32] | Y[PT][RT][32] | X[NB][digit][QT][8]
+    xoff = yoff + PT * RT * 512;
+    slot = xoff + NB * 2 * QT * 128;
+    stages = slot <= 2048 ? 4 : (slot <= 4096 ? 3 : 2);
+    ring = o;  o += kDW * stages * slot;
     coef = o;  o += 4 * nsg * 16;                     // float [a|b|c|d][nsg*4]
     meta = o;  o += NB * 3 * nsg * 16;                // float [NB][scale|sum|l1][nsg*4]
     udig = o;  o += kDW * kGroup * NB * 4 * RT * 32;  // u8 [warps][4 sub][NB][4 slots][RP]
@@ -107,7 +127,13 @@ struct DecodeSmem {
     total = o;
   }
 };
-constexpr int kMaxSgw = 8;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ---- activation preparation ------------------------------------------------------------------
 // One pass over x [M, cw*Q]: per (row m, col patch j) the 16-bit block fixed point digits
@@ -117,7 +143,7 @@ constexpr int kMaxSgw = 8;
 // decode kernel needs no edge tests.  8 lanes share one (m, j) pair.
 template <int QT>
 __global__ void __launch_bounds__(128)
-bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int cw, int Q, int Mp, int cwp,
+bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int cw, int Q, int Mp, int cwp, int NB,
                  uint8_t* __restrict__ xdig, float* __restrict__ xscale, float* __restrict__ xsum,
                  float* __restrict__ xl1) {
   constexpr int QP = QT * 32;
@@ -148,9 +174,9 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
   }
   if (!inside) return;
   const float inv = amax > 0.f ? 32512.f / amax : 0.f;
-  // digit layout [Mp][JG][digit][QT][half][t][sub] words (4 consecutive q each): the 4 col patches of a
-  // super-group are adjacent, so a lane of the decode kernel fetches its B-operand words of a whole
-  // super-group with one 128-bit load per (digit, half)
+  // digit layout [Mp/NB][JG][NB][digit][QT][half][t][sub] words (4 consecutive q each): the rows of an M tile
+  // and the 4 col patches of a super-group are adjacent, so one bulk copy brings a super-group's digits and
+  // a lane of the decode kernel fetches its B-operand words with one 128-bit load per (digit, half)
   const int JG = cwp / kGroup;
   uint32_t* words = reinterpret_cast<uint32_t*>(xdig);
 #pragma unroll
@@ -160,7 +186,7 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
     for (int e = 0; e < 4; ++e) D[e] = (uint32_t)(__float2int_rn(v[w4 * 4 + e] * inv) + 0x8080) ^ 0x8080u;
     const int q4 = sub8 * QT + w4;                 // index of this group of 4 consecutive q
     const int qt = q4 >> 3, half = (q4 >> 2) & 1, tt = q4 & 3;
-    const size_t base = ((size_t)m * JG + (j >> 2)) * 2;
+    const size_t base = (((size_t)(m / NB) * JG + (j >> 2)) * NB + (m % NB)) * 2;
     // x_int = lo + 256*hi with both digits signed bytes
     words[((((base + 0) * QT + qt) * 2 + half) * 4 + tt) * kGroup + (j & 3)] =
         __byte_perm(__byte_perm(D[0], D[1], 0x0040), __byte_perm(D[2], D[3], 0x0040), 0x5410);
@@ -175,21 +201,20 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
 }
 
 template <int PT, int QT, int RT, int NB>
-__global__ void __launch_bounds__(kDT)
+__global__ void __launch_bounds__(kDT, (PT == 1 && NB == 1 ? BQQ_DECODE_MINB : 1))
 bqq_decode_kernel(const DecodeParams p) {
   constexpr int RP = RT * 32;
   constexpr int PP = PT * 32;
   constexpr int NT2 = NB == 1 ? 1 : 2;              // n-tiles of the second contraction
   extern __shared__ __align__(128) uint8_t sm[];
-  const int nsg = kDW * p.sgw;                      // super-groups per chunk (smem row pitch)
+  const int nsg = kDW * p.sgw;                      // super-groups per chunk (pitch of the resident arrays)
   const DecodeSmem L(p.sgw, NB, PT, QT, RT);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L.bars);      // [0..sgw) steps, [kMaxSgw] misc
-  const uint4* zs = reinterpret_cast<const uint4*>(sm + L.zs);
-  const uint4* ys = reinterpret_cast<const uint4*>(sm + L.ys);
-  const uint4* xd = reinterpret_cast<const uint4*>(sm + L.xd);
+  constexpr int S = DecodeSmem(1, NB, PT, QT, RT).stages;
+  constexpr int kSlot = DecodeSmem(1, NB, PT, QT, RT).slot;
+  constexpr int kYoff = DecodeSmem(1, NB, PT, QT, RT).yoff / 16, kXoff = DecodeSmem(1, NB, PT, QT, RT).xoff / 16;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + L.bars);
   const float* scoef = reinterpret_cast<const float*>(sm + L.coef);
   const float* smeta = reinterpret_cast<const float*>(sm + L.meta);
-  uint8_t* udig = sm + L.udig;
   float* red = reinterpret_cast<float*>(sm + L.red);
 
   const int tid = threadIdx.x;
@@ -205,86 +230,157 @@ bqq_decode_kernel(const DecodeParams p) {
   const int m0 = blockIdx.y * NB;
   const int jg0 = chunk * nsg;                      // first col-patch group of the chunk
   const int nvalid = min(nsg, p.JG - jg0);          // super-groups that exist in this chunk
+  const int li0 = warp * p.sgw;                     // this warp's first super-group inside the chunk
+  const int nw = max(0, min(p.sgw, nvalid - li0));  // and how many it owns
   const uint32_t crow = (uint32_t)(((size_t)bit * p.rw + i) * p.cw);   // coefficient row of (bit, i)
   const uint32_t drow = (uint32_t)((size_t)i * p.cw);
 
-  // ---- one thread issues every copy of the CTA; consumers wait on the mbarriers -----------------
+  // ---- ring of this warp: every lane copies 16-byte pieces; a lane's Z and Y pieces are the very
+  // words it will use as tensor core operands, the x digits are shared by the warp ----------------
+  uint4* wring = reinterpret_cast<uint4*>(sm + L.ring + (size_t)warp * S * kSlot);
+  // uint4 per super-group; the 32x32x32 variant is only ever used with one block per plane
+  const int zq = RT * QT == 1 ? 32 : p.RTg * p.QTg * 32, yq = PT * RT == 1 ? 32 : p.PTg * p.RTg * 32;
+  const int RTg = RT == 1 ? 1 : p.RTg, QTg = QT == 1 ? 1 : p.QTg, PTg = PT == 1 ? 1 : p.PTg;
+  constexpr int xq = NB * 2 * QT * 8;
+  const size_t sg0 = (size_t)i * p.NS + (size_t)bit * p.JG + jg0 + li0;
+  const uint4* zsrc = p.zp + sg0 * zq + lane;
+  const uint4* ysrc = p.yp + sg0 * yq + lane;
+  const uint4* xsrc = reinterpret_cast<const uint4*>(p.xdig) + ((size_t)blockIdx.y * p.JG + jg0 + li0) * xq + lane;
+  auto issue_planes = [&](int n) {
+    uint4* dst = wring + (n % S) * (kSlot / 16) + lane;
+#pragma unroll
+    for (int b = 0; b < RT * QT; ++b)
+      if (b * 32 < zq) cp_async16(dst + b * 32, zsrc + (size_t)n * zq + b * 32);
+#pragma unroll
+    for (int b = 0; b < PT * RT; ++b)
+      if (b * 32 < yq) cp_async16(dst + kYoff + b * 32, ysrc + (size_t)n * yq + b * 32);
+  };
+  auto issue_x = [&](int n) {
+    uint4* dst = wring + (n % S) * (kSlot / 16) + kXoff + lane;
+#pragma unroll
+    for (int b = 0; b < (xq + 31) / 32; ++b)
+      if (b * 32 + lane < xq) cp_async16(dst + b * 32, xsrc + (size_t)n * xq + b * 32);
+  };
+
   if (tid == 0) {
-    for (int b = 0; b <= kMaxSgw; ++b) mbar_init(bars + b, 1);
+    mbar_init(bar, 2);
     mbar_init_fence();
+  }
+  // weights first: they do not depend on the activation preparation kernel
+#pragma unroll
+  for (int s = 0; s < S - 1; ++s)
+    if (s < nw) issue_planes(s);
+  __syncthreads();                                   // the barrier is initialised for every waiter
+
+  // ---- coefficients and x statistics of the chunk: bulk copies on the mbarrier ------------------
+  if (lane == 0 && warp == 1) {
     const uint32_t n16 = (uint32_t)nvalid * 16u;                    // bytes of nvalid*4 floats
-    uint32_t misc = NB * (3 * n16 + (uint32_t)nvalid * 2 * QT * 128);
-    if (p.coef_vec) misc += 3 * n16 + (bit == 0 ? n16 : 0u);
-    mbar_expect_tx(bars + kMaxSgw, misc);
-    // weights first: they do not depend on the activation preparation kernel
-    const uint32_t zb = (uint32_t)p.RTg * p.QTg * 512, yb = (uint32_t)p.PTg * p.RTg * 512;   // bytes per super-group
-    const size_t sg0 = (size_t)i * p.NS + (size_t)bit * p.JG + jg0;
-    for (int it = 0; it < p.sgw; ++it) {
-      const int nv = min(kDW, nvalid - kDW * it);
-      if (nv <= 0) break;
-      mbar_expect_tx(bars + it, (uint32_t)nv * (zb + yb));
-      bulk_load(const_cast<uint4*>(zs) + (size_t)it * kDW * (zb / 16), p.zp + (sg0 + kDW * it) * (zb / 16),
-                (uint32_t)nv * zb, bars + it);
-      bulk_load(const_cast<uint4*>(ys) + (size_t)it * kDW * (yb / 16), p.yp + (sg0 + kDW * it) * (yb / 16),
-                (uint32_t)nv * yb, bars + it);
-    }
     if (p.coef_vec) {
+      mbar_expect_tx(bar, 3 * n16 + (bit == 0 ? n16 : 0u));
       float* sc = const_cast<float*>(scoef);
-      bulk_load(sc, reinterpret_cast<const float*>(p.a) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
-      bulk_load(sc + nsg * 4, reinterpret_cast<const float*>(p.b) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
-      bulk_load(sc + nsg * 8, reinterpret_cast<const float*>(p.c) + crow + jg0 * kGroup, n16, bars + kMaxSgw);
+      bulk_load(sc, reinterpret_cast<const float*>(p.a) + crow + jg0 * kGroup, n16, bar);
+      bulk_load(sc + nsg * 4, reinterpret_cast<const float*>(p.b) + crow + jg0 * kGroup, n16, bar);
+      bulk_load(sc + nsg * 8, reinterpret_cast<const float*>(p.c) + crow + jg0 * kGroup, n16, bar);
       if (bit == 0)
-        bulk_load(sc + nsg * 12, reinterpret_cast<const float*>(p.d) + drow + jg0 * kGroup, n16, bars + kMaxSgw);
+        bulk_load(sc + nsg * 12, reinterpret_cast<const float*>(p.d) + drow + jg0 * kGroup, n16, bar);
+    } else {
+      mbar_expect_tx(bar, 0u);
     }
-    // the x digits and statistics come from the preparation kernel launched just before this one
-    // (programmatic dependent launch): wait for it to complete before copying its output
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  // the x digits and statistics come from the preparation kernel launched just before this one
+  // (programmatic dependent launch): wait for it to complete before reading its output
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (lane == 0 && warp == 2) {
+    const uint32_t n16 = (uint32_t)nvalid * 16u;
+    mbar_expect_tx(bar, NB * 3 * n16);
 #pragma unroll
     for (int beta = 0; beta < NB; ++beta) {
       const size_t row = (size_t)(m0 + beta) * p.cwp + (size_t)jg0 * kGroup;
       float* sm_meta = const_cast<float*>(smeta) + beta * 3 * nsg * 4;
-      bulk_load(sm_meta, p.xscale + row, n16, bars + kMaxSgw);
-      bulk_load(sm_meta + nsg * 4, p.xsum + row, n16, bars + kMaxSgw);
-      bulk_load(sm_meta + nsg * 8, p.xl1 + row, n16, bars + kMaxSgw);
-      bulk_load(const_cast<uint4*>(xd) + (size_t)beta * nsg * 2 * QT * 8,
-                reinterpret_cast<const uint4*>(p.xdig) + ((size_t)(m0 + beta) * p.JG + jg0) * 2 * QT * 8,
-                (uint32_t)nvalid * 2 * QT * 128, bars + kMaxSgw);
+      bulk_load(sm_meta, p.xscale + row, n16, bar);
+      bulk_load(sm_meta + nsg * 4, p.xsum + row, n16, bar);
+      bulk_load(sm_meta + nsg * 8, p.xl1 + row, n16, bar);
     }
   }
+  // one copy group per super-group: group k complete means super-group k has arrived
+#pragma unroll
+  for (int s = 0; s < S - 1; ++s) {
+    if (s < nw) issue_x(s);
+    cp_async_commit();
+  }
 
-  // ---- zero the digit exchange buffer (slot 3 of every row must stay zero) --------------------
+  // ---- digit exchange buffer: slots 0..2 are rewritten for every col patch, slot 3 is a column of
+  // ones whose products count the Y bits of each row (removes the offset of the unsigned digits)
   constexpr int kUSub = NB * 4 * RP;                 // bytes of one col patch's u digits
-  uint8_t* my_udig = udig + (size_t)warp * kGroup * kUSub;
-  for (int e = lane; e < kGroup * kUSub / 4; e += 32) reinterpret_cast<uint32_t*>(my_udig)[e] = 0u;
-  __syncthreads();                                   // barriers are initialised for every waiter
-  bool ok = mbar_wait(bars + kMaxSgw, 0);
+  uint8_t* my_udig = sm + L.udig + (size_t)warp * kGroup * kUSub;
+  for (int e = lane; e < kGroup * kUSub / 4; e += 32)
+    reinterpret_cast<uint32_t*>(my_udig)[e] = (((4 * e) / RP) & 3) == 3 ? 0x01010101u : 0u;
+  bool ok = mbar_wait(bar, 0);
 
-  // ---- fixed-point scale of u for this warp: bound |a| sum|x| + |b| |sum x| over its patch-bits
+  // ---- fold the x statistics into the coefficients of this warp's patch-bits (in place of the
+  // statistics):  alpha = a * scale,  beta = b * sum,  gamma = c * scale;  d * sum is summed right
+  // here.  The fixed-point scale of u for this warp comes from the bound |a| sum|x| + |b| |sum x|.
+  constexpr float kUOff = 4128768.f;                 // 63 * 65536: the offset touches the top digit only
+  // float -> integer by mantissa alignment: 2^23 + kUOff + round(u * inv_us); the low three bytes of
+  // the float's bit pattern are then the unsigned base-256 digits of round(u * inv_us) + kUOff
+  constexpr float kMagic = 8388608.f + kUOff;
   const int my_beta = NB == 1 ? 0 : t;
+  float* wmeta = const_cast<float*>(smeta);
   float ub = 0.f;
-  {
-    const int it = lane >> 2, sub = lane & 3;
-    const int sgi = kDW * it + warp;                 // super-group index inside the chunk
-    const int j = (jg0 + sgi) * kGroup + sub;
-    if (it < p.sgw && sgi < nvalid && j < p.cw) {
-      float ca, cb;
-      if (p.coef_vec) {
-        ca = fabsf(scoef[sgi * 4 + sub]);
-        cb = fabsf(scoef[nsg * 4 + sgi * 4 + sub]);
-      } else {
-        ca = fabsf(load_as_float(p.a, crow + j, p.coef_dtype));
-        cb = fabsf(load_as_float(p.b, crow + j, p.coef_dtype));
-      }
+  float dsum[NB];
 #pragma unroll
-      for (int beta = 0; beta < NB; ++beta) {
-        const float* mrow = smeta + beta * 3 * nsg * 4;
-        ub = fmaxf(ub, fmaf(ca, mrow[nsg * 8 + sgi * 4 + sub], cb * fabsf(mrow[nsg * 4 + sgi * 4 + sub])));
+  for (int beta = 0; beta < NB; ++beta) dsum[beta] = 0.f;
+  for (int e = lane; e < nw * kGroup; e += 32) {
+    const int idx = li0 * kGroup + e;                // (super-group, col patch) inside the chunk
+    const int j = jg0 * kGroup + idx;
+    float ca = 0.f, cb = 0.f, cc = 0.f, cd = 0.f;    // ragged last group: zero coefficients
+    if (j < p.cw) {
+      if (p.coef_vec) {
+        ca = scoef[idx];
+        cb = scoef[nsg * 4 + idx];
+        cc = scoef[nsg * 8 + idx];
+        if (bit == 0) cd = scoef[nsg * 12 + idx];
+      } else {
+        ca = load_as_float(p.a, crow + j, p.coef_dtype);
+        cb = load_as_float(p.b, crow + j, p.coef_dtype);
+        cc = load_as_float(p.c, crow + j, p.coef_dtype);
+        if (bit == 0) cd = load_as_float(p.d, drow + j, p.coef_dtype);
       }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ub = fmaxf(ub, __shfl_xor_sync(0xffffffffu, ub, o));
+    for (int beta = 0; beta < NB; ++beta) {
+      float* mr = wmeta + beta * 3 * nsg * 4;
+      const float sc = mr[idx], sx = mr[nsg * 4 + idx], l1 = mr[nsg * 8 + idx];
+      ub = fmaxf(ub, fmaf(fabsf(ca), l1, fabsf(cb * sx)));
+      dsum[beta] = fmaf(cd, sx, dsum[beta]);
+      mr[idx] = ca * sc;
+      mr[nsg * 4 + idx] = cb * sx;
+      mr[nsg * 8 + idx] = cc * sc;
+    }
   }
-  const float inv_us = ub > 0.f ? 4128768.f / ub : 0.f;      // |u| * inv_us < 2^22
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ub = fmaxf(ub, __shfl_xor_sync(0xffffffffu, ub, o));
+  // u * inv_us lies in [-kUOff, kUOff]; adding kUOff makes it a non-negative 23-bit integer
+  const float inv_us = ub > 0.f ? kUOff / ub : 0.f;
+  // second pass over the lane's own entries: alpha *= inv_us, beta = beta * inv_us + magic, so that one
+  // fused multiply-add per rank yields the digits of u
+  for (int e = lane; e < nw * kGroup; e += 32) {
+    const int idx = li0 * kGroup + e;
+#pragma unroll
+    for (int beta = 0; beta < NB; ++beta) {
+      float* mr = wmeta + beta * 3 * nsg * 4;
+      mr[idx] *= inv_us;
+      mr[nsg * 4 + idx] = fmaf(mr[nsg * 4 + idx], inv_us, kMagic);
+    }
+  }
+  float dacc = 0.f;
+#pragma unroll
+  for (int beta = 0; beta < NB; ++beta) {
+    float v = dsum[beta];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (beta == my_beta) dacc = v;
+  }
   __syncwarp();
 
   int acc[PT][2][NT2][4];
@@ -296,88 +392,64 @@ bqq_decode_kernel(const DecodeParams p) {
       for (int nt = 0; nt < NT2; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[pt][mt][nt][e] = 0;
-  float cacc = 0.f, dacc = 0.f;
+  float cacc = 0.f;
   const float rs_t = 1.f / (float)(1 << t);
-  const int e0 = t == 0, e1 = t == 1, e2 = t == 2, e3 = t == 3;
-  const int f0 = e0 << 8, f1 = e1 << 8, f2 = e2 << 8, f3 = e3 << 8;
-  // lane constants: where this lane's B-operand column (n = g) finds its x digits, where the
-  // lane's row of X keeps scale and sum, where its u digits go and come from
-  const uint4* xlane = xd + ((size_t)(NB == 1 ? 0 : (g >> 1)) * nsg * 2 + (g & 1)) * (QT * 8) + t;
-  const float* mrow = smeta + my_beta * 3 * nsg * 4;   // [scale | sum | l1] of this lane's row of X
+  const bool t_odd = (t & 1) != 0, t_hi = (t & 2) != 0;   // lane (g,t) finishes rank g + 8t
+  // lane constants: where this lane's B-operand column (n = g) finds its x digits inside a slot, where
+  // the lane's row of X keeps scale and sum, where its u digits go and come from
+  const int xlane = kXoff + (NB == 1 ? (g & 1) : g) * (QT * 8) + t;
+  const float* mrow = smeta + my_beta * 3 * nsg * 4;   // [alpha | beta | gamma] of this lane's row of X
   uint8_t* ust = my_udig + (NB == 1 ? g + 8 * t : t * 4 * RP + g);
   const uint8_t* uld[NT2];
 #pragma unroll
   for (int nt = 0; nt < NT2; ++nt) {
     const int beta = NB == 1 ? 0 : 2 * nt + (g >> 2);
-    const int slot = NB == 1 ? min(g, 3) : (g & 3);      // slot 3 stays zero
+    const int slot = NB == 1 ? min(g, 3) : (g & 3);      // slot 3: the column of ones
     uld[nt] = my_udig + (beta * 4 + slot) * RP + 4 * t;
   }
-  constexpr float kMagic = 12582912.f;                // 1.5 * 2^23: float -> int by mantissa alignment
-  constexpr uint32_t kUnbias = 0x808080u - 0x4B400000u;
-
-  for (int it = 0; it < p.sgw; ++it) {
-    const int sgi = kDW * it + warp;                  // super-group index inside the chunk
-    if (sgi >= nvalid) break;
-    ok = mbar_wait(bars + it, 0) && ok;
+  for (int n = 0; n < nw; ++n) {
+    // refill the slot consumed in the previous iteration with the super-group S - 1 ahead
+    if (n + S - 1 < nw) {
+      issue_planes(n + S - 1);
+      issue_x(n + S - 1);
+    }
+    cp_async_commit();
+    cp_async_wait<S - 1>();                           // this lane's pieces of super-group n have landed
+    __syncwarp();                                     // ... and every other lane's (x digits, u digit buffer reuse)
+    const uint4* zs = wring + (n % S) * (kSlot / 16);
+    const uint4* ys = zs + kYoff;
+    const int li = li0 + n;                           // super-group index inside the chunk
     // plane words of this super-group
     uint4 zw[RT][QT], yw[PT][RT];
 #pragma unroll
     for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
       for (int qt = 0; qt < QT; ++qt)
-        zw[rt][qt] = (rt < p.RTg && qt < p.QTg) ? zs[((size_t)(sgi * p.RTg + rt) * p.QTg + qt) * 32 + lane]
-                                                  : make_uint4(0u, 0u, 0u, 0u);
+        zw[rt][qt] = (rt < RTg && qt < QTg) ? zs[(rt * QTg + qt) * 32 + lane] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
     for (int pt = 0; pt < PT; ++pt)
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt)
-        yw[pt][rt] = (pt < p.PTg && rt < p.RTg) ? ys[((size_t)(sgi * p.PTg + pt) * p.RTg + rt) * 32 + lane]
-                                                  : make_uint4(0u, 0u, 0u, 0u);
-    // per super-group: coefficients, x scale / sum and the x digit registers of its 4 col patches
-    float ca4[4], cb4[4], cc4[4], cd4[4];
-    if (p.coef_vec) {
-      const float4 va = *reinterpret_cast<const float4*>(scoef + sgi * 4);
-      const float4 vb = *reinterpret_cast<const float4*>(scoef + nsg * 4 + sgi * 4);
-      const float4 vc = *reinterpret_cast<const float4*>(scoef + nsg * 8 + sgi * 4);
-      ca4[0] = va.x; ca4[1] = va.y; ca4[2] = va.z; ca4[3] = va.w;
-      cb4[0] = vb.x; cb4[1] = vb.y; cb4[2] = vb.z; cb4[3] = vb.w;
-      cc4[0] = vc.x; cc4[1] = vc.y; cc4[2] = vc.z; cc4[3] = vc.w;
-      if (bit == 0) {
-        const float4 vd = *reinterpret_cast<const float4*>(scoef + nsg * 12 + sgi * 4);
-        cd4[0] = vd.x; cd4[1] = vd.y; cd4[2] = vd.z; cd4[3] = vd.w;
-      } else {
-        cd4[0] = cd4[1] = cd4[2] = cd4[3] = 0.f;
-      }
-    } else {
-      const uint32_t jb = (uint32_t)(jg0 + sgi) * kGroup;
-#pragma unroll
-      for (int sub = 0; sub < kGroup; ++sub) {
-        const bool in = (int)(jb + sub) < p.cw;          // ragged last group: zero coefficients
-        ca4[sub] = in ? load_as_float(p.a, crow + jb + sub, p.coef_dtype) : 0.f;
-        cb4[sub] = in ? load_as_float(p.b, crow + jb + sub, p.coef_dtype) : 0.f;
-        cc4[sub] = in ? load_as_float(p.c, crow + jb + sub, p.coef_dtype) : 0.f;
-        cd4[sub] = (in && bit == 0) ? load_as_float(p.d, drow + jb + sub, p.coef_dtype) : 0.f;
-      }
-    }
-    const float4 xsc4 = *reinterpret_cast<const float4*>(mrow + sgi * 4);
-    const float4 xs4 = *reinterpret_cast<const float4*>(mrow + nsg * 4 + sgi * 4);
-    const float xscv[4] = {xsc4.x, xsc4.y, xsc4.z, xsc4.w};
-    const float xsv[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
+        yw[pt][rt] = (pt < PTg && rt < RTg) ? ys[(pt * RTg + rt) * 32 + lane] : make_uint4(0u, 0u, 0u, 0u);
+    // per super-group: folded coefficients and the x digit registers of its 4 col patches
+    const float4 va = *reinterpret_cast<const float4*>(mrow + li * 4);
+    const float4 vb = *reinterpret_cast<const float4*>(mrow + nsg * 4 + li * 4);
+    const float4 vc = *reinterpret_cast<const float4*>(mrow + nsg * 8 + li * 4);
+    const float ca4[4] = {va.x, va.y, va.z, va.w};
+    const float cb4[4] = {vb.x, vb.y, vb.z, vb.w};
+    const float cc4[4] = {vc.x, vc.y, vc.z, vc.w};
     uint32_t bx0[kGroup][QT], bx1[kGroup][QT];
 #pragma unroll
     for (int qt = 0; qt < QT; ++qt) {
-      const uint4 h0 = xlane[(size_t)sgi * (2 * QT * 8) + qt * 8];
-      const uint4 h1 = xlane[(size_t)sgi * (2 * QT * 8) + qt * 8 + 4];
+      const uint4 h0 = zs[xlane + qt * 8];
+      const uint4 h1 = zs[xlane + qt * 8 + 4];
       bx0[0][qt] = h0.x; bx0[1][qt] = h0.y; bx0[2][qt] = h0.z; bx0[3][qt] = h0.w;
       bx1[0][qt] = h1.x; bx1[1][qt] = h1.y; bx1[2][qt] = h1.z; bx1[3][qt] = h1.w;
     }
 
 #pragma unroll
     for (int sub = 0; sub < kGroup; ++sub) {
-      const float ca = ca4[sub], cc = cc4[sub];
-      const float xs = xsv[sub];
-      const float bxs = cb4[sub] * xs;
-      dacc = fmaf(cd4[sub], xs, dacc);
+      const float ca = ca4[sub], cb = cb4[sub], cc = cc4[sub];
 
       // ---- first contraction: T[k][digit] = sum_q Z[k][q] xdigit[q] --------------------
 #pragma unroll
@@ -400,26 +472,26 @@ bqq_decode_kernel(const DecodeParams p) {
           }
         }
         if (NB == 1) {
-          // every lane sees (lo, hi) in its two columns; lane (g,t) finishes row k = 32rt + g + 8t
-          // (branch-free: lane constants e_r = [t == r], f_r = 256 e_r pick the row and join the digits)
-          const int I = c1[0][0] * e0 + c1[0][1] * f0 + c1[0][2] * e1 + c1[0][3] * f1 +
-                        c1[1][0] * e2 + c1[1][1] * f2 + c1[1][2] * e3 + c1[1][3] * f3;
-          const float tf = (float)I * (xscv[sub] * rs_t);
+          // every lane sees (lo, hi) in its two columns for ranks g, g+8 (c1[0]) and g+16, g+24 (c1[1]);
+          // lane (g,t) finishes rank k = 32rt + g + 8t
+          const int lo = t_hi ? (t_odd ? c1[1][2] : c1[1][0]) : (t_odd ? c1[0][2] : c1[0][0]);
+          const int hi = t_hi ? (t_odd ? c1[1][3] : c1[1][1]) : (t_odd ? c1[0][3] : c1[0][1]);
+          const float tf = (float)(lo + (hi << 8)) * rs_t;
           cacc = fmaf(cc, tf, cacc);
-          const uint32_t D = ((uint32_t)__float_as_int(fmaf(fmaf(ca, tf, bxs), inv_us, kMagic)) + kUnbias) ^ 0x808080u;
+          const uint32_t D = (uint32_t)__float_as_int(fmaf(ca, tf, cb));
           uint8_t* dst = ust + sub * kUSub + rt * 32;
           dst[0] = (uint8_t)D;
           dst[RP] = (uint8_t)(D >> 8);
           dst[2 * RP] = (uint8_t)(D >> 16);
         } else {
-          // lane (g,t) owns row t of X: finishes rows k = 32rt + g + 8rr, rr = 0..3
+          // lane (g,t) owns row t of X: finishes ranks k = 32rt + g + 8rr, rr = 0..3
 #pragma unroll
           for (int rr = 0; rr < 4; ++rr) {
             const int lo = c1[rr >> 1][2 * (rr & 1)];
             const int hi = c1[rr >> 1][2 * (rr & 1) + 1];
-            const float tf = (float)(lo + (hi << 8)) * (xscv[sub] * (1.f / (float)(1 << rr)));
+            const float tf = (float)(lo + (hi << 8)) * (1.f / (float)(1 << rr));
             cacc = fmaf(cc, tf, cacc);
-            const uint32_t D = ((uint32_t)__float_as_int(fmaf(fmaf(ca, tf, bxs), inv_us, kMagic)) + kUnbias) ^ 0x808080u;
+            const uint32_t D = (uint32_t)__float_as_int(fmaf(ca, tf, cb));
             uint8_t* dst = ust + sub * kUSub + rt * 32 + 8 * rr;
             dst[0] = (uint8_t)D;
             dst[RP] = (uint8_t)(D >> 8);
@@ -447,16 +519,16 @@ bqq_decode_kernel(const DecodeParams p) {
           const uint32_t w4 = w >> 4;
 #pragma unroll
           for (int nt = 0; nt < NT2; ++nt) {
-            mma_u8s8(acc[pt][0][nt], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
+            mma_u8u8(acc[pt][0][nt], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
                      bu[nt][0], bu[nt][1]);
-            mma_u8s8(acc[pt][1][nt], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
+            mma_u8u8(acc[pt][1][nt], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
                      bu[nt][0], bu[nt][1]);
           }
         }
       }
     }
-    __syncwarp();
   }
+  cp_async_wait<0>();
 
   if (!ok && lane == 0) atomicExch(p.counters + (kMaxCounters - 1), 1u);   // a bounded wait gave up
 
@@ -471,14 +543,16 @@ bqq_decode_kernel(const DecodeParams p) {
     for (int o = 16; o >= 4; o >>= 1) cterm += __shfl_xor_sync(0xffffffffu, cterm, o);   // lanes with equal t
   }
   cterm += dacc;
-  const float us = ub * (1.f / 4128768.f);
+  const float us = ub * (1.f / kUOff);
 #pragma unroll
   for (int nt = 0; nt < NT2; ++nt) {
-    // which row of X and which digits this lane's two columns carry
+    // which row of X and which digits this lane's two columns carry: (digit 0, digit 1) or
+    // (digit 2, ones); the ones column times 63 removes the offset from the top digit exactly
     const int beta = NB == 1 ? 0 : 2 * nt + (t >> 1);
     const int tt = NB == 1 ? t : (t & 1);
     const float w_even = tt == 0 ? 1.f : (tt == 1 ? 65536.f : 0.f);
     const float w_odd = tt == 0 ? 256.f : 0.f;
+    const int k63 = tt == 1 ? 63 : 0;
     const float ct_b = NB == 1 ? cterm : __shfl_sync(0xffffffffu, cterm, (lane & ~3) | beta);
 #pragma unroll
     for (int pt = 0; pt < PT; ++pt)
@@ -487,7 +561,8 @@ bqq_decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int rr = 2 * mt + half;
-          float v = w_even * (float)acc[pt][mt][nt][2 * half] + w_odd * (float)acc[pt][mt][nt][2 * half + 1];
+          const int a_even = acc[pt][mt][nt][2 * half], a_odd = acc[pt][mt][nt][2 * half + 1];
+          float v = w_even * (float)(a_even - k63 * a_odd) + w_odd * (float)a_odd;
           v += __shfl_xor_sync(0xffffffffu, v, 1);
           if (NB == 1) v += __shfl_xor_sync(0xffffffffu, v, 2);
           const float out = fmaf(v, us * (1.f / (float)(1 << rr)), ct_b);
@@ -495,15 +570,22 @@ bqq_decode_kernel(const DecodeParams p) {
           if (writer) red[(size_t)(warp * NB + beta) * PP + pt * 32 + g + 8 * rr] = out;
         }
   }
-  __syncthreads();
 
-  // ---- CTA result, then the cross-CTA reduction in a fixed order ----------------------------
+  // ---- warps 1..3 hand their sums to warp 0 and retire ---------------------------------------
+  __threadfence_block();
+  if (warp != 0) {
+    asm volatile("bar.arrive 1, %0;" ::"n"(kDT) : "memory");
+    return;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kDT) : "memory");
+
+  // ---- CTA result, then the cross-CTA reduction in a fixed order (warp 0) ---------------------
   const int nparts = p.bw * p.nchunks;
   const int part = bit * p.nchunks + chunk;
   const int mrows = p.mtiles * NB;
   const size_t out_stride = (size_t)p.rw * PP;
   if (nparts == 1) {
-    for (int idx = tid; idx < NB * PP; idx += kDT) {
+    for (int idx = lane; idx < NB * PP; idx += 32) {
       const int beta = idx / PP, pp = idx % PP;
       float v = 0.f;
 #pragma unroll
@@ -516,21 +598,25 @@ bqq_decode_kernel(const DecodeParams p) {
     }
     return;
   }
-  for (int idx = tid; idx < NB * PP; idx += kDT) {
+  for (int idx = lane; idx < NB * PP; idx += 32) {
     const int beta = idx / PP, pp = idx % PP;
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < kDW; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
     p.partial[((size_t)part * mrows + m0 + beta) * out_stride + (size_t)i * PP + pp] = v;
   }
-  __threadfence();
-  __syncthreads();
-  __shared__ unsigned ticket;
-  if (tid == 0) ticket = atomicAdd(p.counters + i * p.mtiles + blockIdx.y, 1u);
-  __syncthreads();
+  // the lanes' partial sums are ordered before lane 0's fence by the warp barrier, the fence before
+  // the ticket; the CTA that draws the last ticket sees every other CTA's partial sums
+  __syncwarp();
+  unsigned ticket = 0;
+  if (lane == 0) {
+    __threadfence();
+    ticket = atomicAdd(p.counters + i * p.mtiles + blockIdx.y, 1u);
+    __threadfence();
+  }
+  ticket = __shfl_sync(0xffffffffu, ticket, 0);
   if (ticket != (unsigned)(nparts - 1)) return;
-  __threadfence();
-  for (int idx = tid; idx < NB * PP; idx += kDT) {
+  for (int idx = lane; idx < NB * PP; idx += 32) {
     const int beta = idx / PP, pp = idx % PP;
     if (pp < p.P && m0 + beta < p.M) {
       float v = 0.f;
@@ -541,7 +627,7 @@ bqq_decode_kernel(const DecodeParams p) {
       store_from_float(p.y, (size_t)(m0 + beta) * p.ldy + o, p.y_dtype, v);
     }
   }
-  if (tid == 0) p.counters[i * p.mtiles + blockIdx.y] = 0u;   // ready for the next call
+  if (lane == 0) p.counters[i * p.mtiles + blockIdx.y] = 0u;   // ready for the next call
 }
 
 template <int PT, int QT, int RT, int NB>
@@ -553,7 +639,7 @@ static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cu
   }
   const int pairs = p.Mp * p.cwp;
   bqq_xprep_kernel<QT><<<(pairs * 8 + 127) / 128, 128, 0, st>>>(
-      p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, const_cast<uint8_t*>(p.xdig),
+      p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, NB, const_cast<uint8_t*>(p.xdig),
       const_cast<float*>(p.xscale), const_cast<float*>(p.xsum), const_cast<float*>(p.xl1));
   // decode kernel: programmatic dependent launch after the preparation kernel, so that its weight
   // copies overlap the preparation; the kernel itself waits before it touches the prepared x
