@@ -1,7 +1,5 @@
 // Host side of the decode forward: launch plan and dispatch to the kernel variants
 // (algorithm and kernel in bqq_decode_kernel.cuh).
-#include <stdlib.h>
-
 #include "bqq_decode_kernel.cuh"
 
 namespace bqq {
@@ -16,7 +14,6 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 static const int kVariantPT[4] = {1, 2, 2, 4};
 static const int kVariantQT[4] = {1, 2, 2, 4};
 static const int kVariantRT[4] = {1, 1, 2, 2};
-static const int kVariantMaxSgw[4] = {32, 16, 8, 4};
 
 // The plan depends on the patch geometry, the number of col patches and M only
 // (never on the number of row patches), so row shards reduce in the same order.
@@ -28,9 +25,12 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   if (pl.variant < 0) { pl.smem = 0; return pl; }
   pl.NB = M <= 1 ? 1 : 4;
   pl.mtiles = (M + pl.NB - 1) / pl.NB;
-  int sgw = g.JG <= 16 ? 1 : (g.JG <= 48 ? 2 : (g.JG <= 96 ? 4 : 8));
-  if (const char* e = getenv("BQQ_DECODE_SGW")) sgw = atoi(e);
-  if (sgw > kVariantMaxSgw[pl.variant]) sgw = kVariantMaxSgw[pl.variant];
+  // chunks per (row patch, bit layer): long chunks amortise the per-warp set-up, two chunks keep enough
+  // CTAs in flight on wide layers (measured on 2048..14336 input features)
+  int nchunks = g.JG <= 32 ? 1 : (g.JG <= 128 ? 2 : (g.JG + 63) / 64);
+  if (pl.NB > 1 && g.JG > 64) nchunks = (g.JG + 31) / 32;   // batched rows: shorter chunks balance better
+  int sgw = (g.JG + kDW * nchunks - 1) / (kDW * nchunks);
+  if (sgw > kMaxSgw) sgw = kMaxSgw;
   pl.sgw = sgw;
   pl.nchunks = (g.JG + kDW * sgw - 1) / (kDW * sgw);
   pl.nparts = g.bw * pl.nchunks;

@@ -103,7 +103,7 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int sub) {
   return sub == 0 ? v.x : (sub == 1 ? v.y : (sub == 2 ? v.z : v.w));
 }
 
-constexpr int kMaxSgw = 64;              // upper bound of super-groups per warp (resident coefficients: 64 B each)
+constexpr int kMaxSgw = 32;              // upper bound of super-groups per warp (resident coefficients: 64 B each)
 
 // Shared-memory carve-up (bytes), shared by host plan and kernel.  Per warp a ring of `stages`
 // slots, each holding one super-group: its Z words, Y words and the x digits of the CTA's rows.
