@@ -407,6 +407,7 @@ bqq_decode_kernel(const DecodeParams p) {
     const int slot = NB == 1 ? min(g, 3) : (g & 3);      // slot 3: the column of ones
     uld[nt] = my_udig + (beta * 4 + slot) * RP + 4 * t;
   }
+#pragma unroll(NB == 1 ? 4 : 1)
   for (int n = 0; n < nw; ++n) {
     // refill the slot consumed in the previous iteration with the super-group S - 1 ahead
     if (n + S - 1 < nw) {
