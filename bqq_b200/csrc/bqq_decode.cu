@@ -33,9 +33,12 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   if (sgw > kMaxSgw) sgw = kMaxSgw;
   pl.sgw = sgw;
   pl.nchunks = (g.JG + kDW * sgw - 1) / (kDW * sgw);
-  pl.nparts = g.bw * pl.nchunks;
+  // short single-chunk layers at batch 1: one CTA takes all bit layers of a row patch, so the sums never
+  // leave the CTA (no scratch round trip); 4 warps per bit layer, at most 16 warps
+  pl.bpc = (pl.variant == 0 && pl.NB == 1 && pl.nchunks == 1 && g.bw <= 4) ? g.bw : 1;
+  pl.nparts = (g.bw / pl.bpc) * pl.nchunks;
   const int PTv = kVariantPT[pl.variant], QTv = kVariantQT[pl.variant], RTv = kVariantRT[pl.variant];
-  pl.smem = (size_t)DecodeSmem(sgw, pl.NB, PTv, QTv, RTv).total;
+  pl.smem = (size_t)DecodeSmem(sgw, pl.NB, PTv, QTv, RTv, pl.bpc).total;
   const size_t Mp = (size_t)pl.mtiles * pl.NB, cwp = (size_t)g.JG * kGroup;
   pl.xdig_bytes = align_up(Mp * cwp * 2 * QTv * 32, 256);
   pl.xmeta_bytes = 3 * align_up(Mp * cwp * 4, 256);     // scale, sum, l1
@@ -68,7 +71,7 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
   p.x_dtype = x_dtype; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
   p.M = M; p.bw = g.bw; p.rw = g.rw; p.cw = g.cw; p.P = g.P; p.Q = g.Q;
   p.PTg = g.PT; p.QTg = g.QT; p.RTg = g.RT; p.JG = g.JG; p.NS = g.NS;
-  p.sgw = pl.sgw; p.nchunks = pl.nchunks; p.mtiles = pl.mtiles;
+  p.sgw = pl.sgw; p.bpc = pl.bpc; p.nchunks = pl.nchunks; p.mtiles = pl.mtiles;
   const size_t need = decode_workspace_bytes(&L->dims, M);
   if (!ws || ws_bytes < need) return BQQ_ERR_WORKSPACE;
   if (((uintptr_t)ws & 255) != 0) return BQQ_ERR_MISALIGNED;

@@ -33,9 +33,6 @@
 
 namespace bqq {
 
-#ifndef BQQ_DECODE_MINB
-#define BQQ_DECODE_MINB 6
-#endif
 constexpr int kDW = 4;                   // warps per CTA
 constexpr int kDT = kDW * 32;
 constexpr int kMaxCounters = 65536;      // fixed-size counter region at the start of the workspace
@@ -46,6 +43,7 @@ struct DecodePlan {
   int NB;          // rows of X per CTA: 1 or 4
   int mtiles;      // ceil(M / NB)
   int sgw;         // super-groups per warp
+  int bpc;         // bit layers per CTA (kDW warps each): 1, or all of them for short single-chunk layers
   int nchunks;     // chunks per bit layer
   int nparts;      // partial sums per output = bw * nchunks
   size_t smem;
@@ -72,7 +70,7 @@ struct DecodeParams {
   int M, bw, rw, cw, P, Q;
   int PTg, QTg, RTg;       // 32-blocks of the planes as packed
   int JG, NS;
-  int sgw, nchunks, mtiles;
+  int sgw, nchunks, mtiles, bpc;
   int coef_vec;            // 1: fp32 coefficients, cw % 4 == 0, 16-byte aligned -> 128-bit loads
 };
 
@@ -109,21 +107,26 @@ constexpr int kMaxSgw = 32;              // upper bound of super-groups per warp
 // slots, each holding one super-group: its Z words, Y words and the x digits of the CTA's rows.
 // Resident for the whole chunk: coefficients and x statistics (one mbarrier).
 struct DecodeSmem {
-  int bars, ring, slot, stages, yoff, xoff, coef, meta, udig, red, total;
-  __host__ __device__ constexpr DecodeSmem(int sgw, int NB, int PT, int QT, int RT)
-      : bars(0), ring(0), slot(0), stages(0), yoff(0), xoff(0), coef(0), meta(0), udig(0), red(0), total(0) {
+  int bars, ring, slot, stages, yoff, xoff, coef, meta, udig, red, xres, xstat, total;
+  __host__ __device__ constexpr DecodeSmem(int sgw, int NB, int PT, int QT, int RT, int bpc = 1)
+      : bars(0), ring(0), slot(0), stages(0), yoff(0), xoff(0), coef(0), meta(0), udig(0), red(0), xres(0), xstat(0),
+        total(0) {
     const int nsg = kDW * sgw;                        // super-groups per chunk
+    const int nwarps = kDW * bpc;
     int o = 0;
-    bars = o;  o += 128;                              // one mbarrier
+    bars = o;  o += 128;                              // one mbarrier per bit layer of the CTA
     yoff = RT * QT * 512;                             // slot: uint4 Z[RT][QT][32] | Y[PT][RT][32] | X[NB][digit][QT][8]
     xoff = yoff + PT * RT * 512;
     slot = xoff + NB * 2 * QT * 128;
     stages = slot <= 2048 ? 4 : (slot <= 4096 ? 3 : 2);
-    ring = o;  o += kDW * stages * slot;
-    coef = o;  o += 4 * nsg * 16;                     // float [a|b|c|d][nsg*4]
-    meta = o;  o += NB * 3 * nsg * 16;                // float [NB][scale|sum|l1][nsg*4]
-    udig = o;  o += kDW * kGroup * NB * 4 * RT * 32;  // u8 [warps][4 sub][NB][4 slots][RP]
-    red = o;   o += kDW * NB * PT * 32 * 4;           // f32 [warps][NB][PP]
+    ring = o;  o += nwarps * stages * slot;
+    coef = o;  o += bpc * 4 * nsg * 16;               // float [bit][a|b|c|d][nsg*4]
+    meta = o;  o += bpc * NB * 3 * nsg * 16;          // float [bit][NB][scale|sum|l1][nsg*4]
+    udig = o;  o += nwarps * kGroup * NB * 4 * RT * 32;  // u8 [warps][4 sub][NB][4 slots][RP]
+    red = o;   o += nwarps * NB * PT * 32 * 4;        // f32 [warps][NB][PP]
+    // CTAs that take all bit layers prepare x themselves: digits and statistics of the whole chunk
+    xres = o;  o += bpc > 1 ? nsg * NB * 2 * QT * 128 : 0;   // uint4 [nsg][NB][digit][QT][8]
+    xstat = o; o += bpc > 1 ? 3 * nsg * 16 : 0;              // float [scale|sum|l1][nsg*4]
     total = o;
   }
 };
@@ -141,21 +144,15 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // and xscale / xsum / xl1 [Mp][cwp] = scale, sum_q x, sum_q |x|.  Rows m >= M and col patches
 // j >= cw (Mp, cwp: M and cw rounded up to the kernel's tiles) are written as zeros so that the
 // decode kernel needs no edge tests.  8 lanes share one (m, j) pair.
+// Body shared by the preparation kernel and the decode kernel that prepares x itself: one
+// (row, col patch) pair per 8 lanes.  `live` pairs read x[m, j*Q ...]; the others write zeros.
+// Digits go to words[] at the pair's place (M tile `mtile`, row `beta` inside it), statistics to
+// index `stat` of xscale / xsum / xl1.  Every lane of the warp must call it (shuffles).
 template <int QT>
-__global__ void __launch_bounds__(128)
-bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int cw, int Q, int Mp, int cwp, int NB,
-                 uint8_t* __restrict__ xdig, float* __restrict__ xscale, float* __restrict__ xsum,
-                 float* __restrict__ xl1) {
-  constexpr int QP = QT * 32;
-  // the decode kernel of this layer may start now: it first streams its weight planes and only
-  // then waits (griddepcontrol.wait) for this grid to finish
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int sub8 = threadIdx.x & 7;
-  const int pairs = Mp * cwp;
-  const int pair = (blockIdx.x * 128 + threadIdx.x) >> 3;
-  const bool inside = pair < pairs;
-  const int m = inside ? pair / cwp : 0, j = inside ? pair % cwp : 0;
-  const bool live = inside && m < M && j < cw;
+__device__ __forceinline__ void xprep_pair(const void* __restrict__ x, int x_dtype, int64_t ldx, int Q, int NB, int JG,
+                                           bool write, bool live, int m, int j, int mtile, int beta, int sub8,
+                                           uint32_t* __restrict__ words, float* __restrict__ xscale,
+                                           float* __restrict__ xsum, float* __restrict__ xl1, int stat) {
   float v[4 * QT];
   float amax = 0.f, sum = 0.f, l1 = 0.f;
 #pragma unroll
@@ -172,13 +169,11 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
     sum += __shfl_xor_sync(0xffffffffu, sum, o);
     l1 += __shfl_xor_sync(0xffffffffu, l1, o);
   }
-  if (!inside) return;
+  if (!write) return;
   const float inv = amax > 0.f ? 32512.f / amax : 0.f;
-  // digit layout [Mp/NB][JG][NB][digit][QT][half][t][sub] words (4 consecutive q each): the rows of an M tile
-  // and the 4 col patches of a super-group are adjacent, so one bulk copy brings a super-group's digits and
+  // digit layout [M tile][JG][NB][digit][QT][half][t][sub] words (4 consecutive q each): the rows of an M tile
+  // and the 4 col patches of a super-group are adjacent, so one run of copies brings a super-group's digits and
   // a lane of the decode kernel fetches its B-operand words with one 128-bit load per (digit, half)
-  const int JG = cwp / kGroup;
-  uint32_t* words = reinterpret_cast<uint32_t*>(xdig);
 #pragma unroll
   for (int w4 = 0; w4 < QT; ++w4) {
     uint32_t D[4];
@@ -186,7 +181,7 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
     for (int e = 0; e < 4; ++e) D[e] = (uint32_t)(__float2int_rn(v[w4 * 4 + e] * inv) + 0x8080) ^ 0x8080u;
     const int q4 = sub8 * QT + w4;                 // index of this group of 4 consecutive q
     const int qt = q4 >> 3, half = (q4 >> 2) & 1, tt = q4 & 3;
-    const size_t base = (((size_t)(m / NB) * JG + (j >> 2)) * NB + (m % NB)) * 2;
+    const size_t base = (((size_t)mtile * JG + (j >> 2)) * NB + beta) * 2;
     // x_int = lo + 256*hi with both digits signed bytes
     words[((((base + 0) * QT + qt) * 2 + half) * 4 + tt) * kGroup + (j & 3)] =
         __byte_perm(__byte_perm(D[0], D[1], 0x0040), __byte_perm(D[2], D[3], 0x0040), 0x5410);
@@ -194,43 +189,64 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
         __byte_perm(__byte_perm(D[0], D[1], 0x0051), __byte_perm(D[2], D[3], 0x0051), 0x5410);
   }
   if (sub8 == 0) {
-    xscale[pair] = amax * (1.f / 32512.f);
-    xsum[pair] = sum;
-    xl1[pair] = l1;
+    xscale[stat] = amax * (1.f / 32512.f);
+    xsum[stat] = sum;
+    xl1[stat] = l1;
   }
 }
 
-template <int PT, int QT, int RT, int NB>
-__global__ void __launch_bounds__(kDT, (PT == 1 && NB == 1 ? BQQ_DECODE_MINB : 1))
+template <int QT>
+__global__ void __launch_bounds__(128)
+bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int cw, int Q, int Mp, int cwp, int NB,
+                 uint8_t* __restrict__ xdig, float* __restrict__ xscale, float* __restrict__ xsum,
+                 float* __restrict__ xl1) {
+  // the decode kernel of this layer may start now: it first streams its weight planes and only
+  // then waits (griddepcontrol.wait) for this grid to finish
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int pairs = Mp * cwp;
+  const int pair = (blockIdx.x * 128 + threadIdx.x) >> 3;
+  const bool inside = pair < pairs;
+  const int m = inside ? pair / cwp : 0, j = inside ? pair % cwp : 0;
+  xprep_pair<QT>(x, x_dtype, ldx, Q, NB, cwp / kGroup, inside, inside && m < M && j < cw, m, j, m / NB, m % NB,
+                 threadIdx.x & 7, reinterpret_cast<uint32_t*>(xdig), xscale, xsum, xl1, pair);
+}
+
+// MB: the CTA takes all bit layers of its row patch (4 warps each) instead of one.
+template <int PT, int QT, int RT, int NB, bool MB>
+__global__ void __maxnreg__(PT == 1 && NB == 1 ? 80 : 255)
 bqq_decode_kernel(const DecodeParams p) {
+  const int bpc = MB ? p.bpc : 1;
   constexpr int RP = RT * 32;
   constexpr int PP = PT * 32;
   constexpr int NT2 = NB == 1 ? 1 : 2;              // n-tiles of the second contraction
   extern __shared__ __align__(128) uint8_t sm[];
   const int nsg = kDW * p.sgw;                      // super-groups per chunk (pitch of the resident arrays)
-  const DecodeSmem L(p.sgw, NB, PT, QT, RT);
+  const DecodeSmem L(p.sgw, NB, PT, QT, RT, bpc);
   constexpr int S = DecodeSmem(1, NB, PT, QT, RT).stages;
   constexpr int kSlot = DecodeSmem(1, NB, PT, QT, RT).slot;
   constexpr int kYoff = DecodeSmem(1, NB, PT, QT, RT).yoff / 16, kXoff = DecodeSmem(1, NB, PT, QT, RT).xoff / 16;
-  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + L.bars);
-  const float* scoef = reinterpret_cast<const float*>(sm + L.coef);
-  const float* smeta = reinterpret_cast<const float*>(sm + L.meta);
-  float* red = reinterpret_cast<float*>(sm + L.red);
-
   const int tid = threadIdx.x;
   const int lane = tid & 31;
-  const int warp = tid >> 5;
+  const int warp = tid >> 5;                        // CTA-wide: ring, digit buffer, sums
+  const int wq = MB ? warp % kDW : warp;            // position inside the chunk
+  const int bq = MB ? warp / kDW : 0;               // bit layer inside the CTA's group
   const int g = lane >> 2;
   const int t = lane & 3;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sm + L.bars) + bq;
+  const float* scoef = reinterpret_cast<const float*>(sm + L.coef) + bq * 4 * nsg * 4;
+  const float* smeta = reinterpret_cast<const float*>(sm + L.meta) + bq * NB * 3 * nsg * 4;
+  float* red = reinterpret_cast<float*>(sm + L.red);
 
   int bid = blockIdx.x;
+  const int nbg = p.bw / bpc;                       // bit groups
   const int chunk = bid % p.nchunks; bid /= p.nchunks;
-  const int bit = bid % p.bw;
-  const int i = bid / p.bw;
+  const int bitgroup = bid % nbg;
+  const int bit = bitgroup * bpc + bq;
+  const int i = bid / nbg;
   const int m0 = blockIdx.y * NB;
   const int jg0 = chunk * nsg;                      // first col-patch group of the chunk
   const int nvalid = min(nsg, p.JG - jg0);          // super-groups that exist in this chunk
-  const int li0 = warp * p.sgw;                     // this warp's first super-group inside the chunk
+  const int li0 = wq * p.sgw;                       // this warp's first super-group inside the chunk
   const int nw = max(0, min(p.sgw, nvalid - li0));  // and how many it owns
   const uint32_t crow = (uint32_t)(((size_t)bit * p.rw + i) * p.cw);   // coefficient row of (bit, i)
   const uint32_t drow = (uint32_t)((size_t)i * p.cw);
@@ -263,7 +279,7 @@ bqq_decode_kernel(const DecodeParams p) {
   };
 
   if (tid == 0) {
-    mbar_init(bar, 2);
+    for (int b = 0; b < bpc; ++b) mbar_init(bar + b, MB ? 1 : 2);
     mbar_init_fence();
   }
   // weights first: they do not depend on the activation preparation kernel
@@ -273,7 +289,7 @@ bqq_decode_kernel(const DecodeParams p) {
   __syncthreads();                                   // the barrier is initialised for every waiter
 
   // ---- coefficients and x statistics of the chunk: bulk copies on the mbarrier ------------------
-  if (lane == 0 && warp == 1) {
+  if (lane == 0 && wq == 1) {
     const uint32_t n16 = (uint32_t)nvalid * 16u;                    // bytes of nvalid*4 floats
     if (p.coef_vec) {
       mbar_expect_tx(bar, 3 * n16 + (bit == 0 ? n16 : 0u));
@@ -287,10 +303,21 @@ bqq_decode_kernel(const DecodeParams p) {
       mbar_expect_tx(bar, 0u);
     }
   }
-  // the x digits and statistics come from the preparation kernel launched just before this one
-  // (programmatic dependent launch): wait for it to complete before reading its output
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (lane == 0 && warp == 2) {
+  const uint4* xres = reinterpret_cast<const uint4*>(sm + L.xres);      // MB only
+  const float* xstat = reinterpret_cast<const float*>(sm + L.xstat);    // MB only
+  if (MB) {
+    // this CTA prepares x itself (no preparation kernel was launched): every 8 lanes take one col patch
+    float* st = const_cast<float*>(xstat);
+    for (int pair = tid >> 3; pair < nsg * kGroup; pair += (kDT * bpc) >> 3)
+      xprep_pair<QT>(p.x, p.x_dtype, p.ldx, p.Q, NB, nsg, true, pair < p.cw && m0 < p.M, m0, pair, 0, 0, tid & 7,
+                     reinterpret_cast<uint32_t*>(sm + L.xres), st, st + nsg * 4, st + nsg * 8, pair);
+    __syncthreads();
+  } else {
+    // the x digits and statistics come from the preparation kernel launched just before this one
+    // (programmatic dependent launch): wait for it to complete before reading its output
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
+  if (!MB && lane == 0 && wq == 2) {
     const uint32_t n16 = (uint32_t)nvalid * 16u;
     mbar_expect_tx(bar, NB * 3 * n16);
 #pragma unroll
@@ -305,7 +332,7 @@ bqq_decode_kernel(const DecodeParams p) {
   // one copy group per super-group: group k complete means super-group k has arrived
 #pragma unroll
   for (int s = 0; s < S - 1; ++s) {
-    if (s < nw) issue_x(s);
+    if (!MB && s < nw) issue_x(s);
     cp_async_commit();
   }
 
@@ -350,7 +377,8 @@ bqq_decode_kernel(const DecodeParams p) {
 #pragma unroll
     for (int beta = 0; beta < NB; ++beta) {
       float* mr = wmeta + beta * 3 * nsg * 4;
-      const float sc = mr[idx], sx = mr[nsg * 4 + idx], l1 = mr[nsg * 8 + idx];
+      const float* raw = MB ? xstat : mr;              // MB: statistics shared by the CTA's bit layers
+      const float sc = raw[idx], sx = raw[nsg * 4 + idx], l1 = raw[nsg * 8 + idx];
       ub = fmaxf(ub, fmaf(fabsf(ca), l1, fabsf(cb * sx)));
       dsum[beta] = fmaf(cd, sx, dsum[beta]);
       mr[idx] = ca * sc;
@@ -412,7 +440,7 @@ bqq_decode_kernel(const DecodeParams p) {
     // refill the slot consumed in the previous iteration with the super-group S - 1 ahead
     if (n + S - 1 < nw) {
       issue_planes(n + S - 1);
-      issue_x(n + S - 1);
+      if (!MB) issue_x(n + S - 1);
     }
     cp_async_commit();
     cp_async_wait<S - 1>();                           // this lane's pieces of super-group n have landed
@@ -442,8 +470,9 @@ bqq_decode_kernel(const DecodeParams p) {
     uint32_t bx0[kGroup][QT], bx1[kGroup][QT];
 #pragma unroll
     for (int qt = 0; qt < QT; ++qt) {
-      const uint4 h0 = zs[xlane + qt * 8];
-      const uint4 h1 = zs[xlane + qt * 8 + 4];
+      const uint4* xd = MB ? xres + li * xq - kXoff : zs;   // MB: digits of the whole chunk are resident
+      const uint4 h0 = xd[xlane + qt * 8];
+      const uint4 h1 = xd[xlane + qt * 8 + 4];
       bx0[0][qt] = h0.x; bx0[1][qt] = h0.y; bx0[2][qt] = h0.z; bx0[3][qt] = h0.w;
       bx1[0][qt] = h1.x; bx1[1][qt] = h1.y; bx1[2][qt] = h1.z; bx1[3][qt] = h1.w;
     }
@@ -572,25 +601,26 @@ bqq_decode_kernel(const DecodeParams p) {
         }
   }
 
-  // ---- warps 1..3 hand their sums to warp 0 and retire ---------------------------------------
+  // ---- the other warps hand their sums to warp 0 and retire ----------------------------------
   __threadfence_block();
+  const int nthreads = kDT * bpc;
   if (warp != 0) {
-    asm volatile("bar.arrive 1, %0;" ::"n"(kDT) : "memory");
+    asm volatile("bar.arrive 1, %0;" ::"r"(nthreads) : "memory");
     return;
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kDT) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 
   // ---- CTA result, then the cross-CTA reduction in a fixed order (warp 0) ---------------------
-  const int nparts = p.bw * p.nchunks;
-  const int part = bit * p.nchunks + chunk;
+  const int nparts = nbg * p.nchunks;
+  const int part = bitgroup * p.nchunks + chunk;
+  const int nwarps = kDW * bpc;
   const int mrows = p.mtiles * NB;
   const size_t out_stride = (size_t)p.rw * PP;
   if (nparts == 1) {
     for (int idx = lane; idx < NB * PP; idx += 32) {
       const int beta = idx / PP, pp = idx % PP;
       float v = 0.f;
-#pragma unroll
-      for (int w = 0; w < kDW; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
+      for (int w = 0; w < nwarps; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
       if (pp < p.P && m0 + beta < p.M) {
         const int o = i * p.P + pp;
         if (p.bias) v += load_as_float(p.bias, o, p.bias_dtype);
@@ -602,8 +632,7 @@ bqq_decode_kernel(const DecodeParams p) {
   for (int idx = lane; idx < NB * PP; idx += 32) {
     const int beta = idx / PP, pp = idx % PP;
     float v = 0.f;
-#pragma unroll
-    for (int w = 0; w < kDW; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
+    for (int w = 0; w < nwarps; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
     p.partial[((size_t)part * mrows + m0 + beta) * out_stride + (size_t)i * PP + pp] = v;
   }
   // the lanes' partial sums are ordered before lane 0's fence by the warp barrier, the fence before
@@ -633,27 +662,31 @@ bqq_decode_kernel(const DecodeParams p) {
 
 template <int PT, int QT, int RT, int NB>
 static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cudaStream_t st) {
-  auto kern = bqq_decode_kernel<PT, QT, RT, NB>;
+  auto kern = (PT == 1 && NB == 1 && p.bpc > 1) ? bqq_decode_kernel<PT, QT, RT, NB, (PT == 1 && NB == 1)>
+                                                : bqq_decode_kernel<PT, QT, RT, NB, false>;
   if (pl.smem > 48 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
       return BQQ_ERR_CUDA;
   }
-  const int pairs = p.Mp * p.cwp;
-  bqq_xprep_kernel<QT><<<(pairs * 8 + 127) / 128, 128, 0, st>>>(
-      p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, NB, const_cast<uint8_t*>(p.xdig),
-      const_cast<float*>(p.xscale), const_cast<float*>(p.xsum), const_cast<float*>(p.xl1));
+  const bool merged = PT == 1 && NB == 1 && p.bpc > 1;   // such CTAs prepare x themselves
+  if (!merged) {
+    const int pairs = p.Mp * p.cwp;
+    bqq_xprep_kernel<QT><<<(pairs * 8 + 127) / 128, 128, 0, st>>>(
+        p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, NB, const_cast<uint8_t*>(p.xdig),
+        const_cast<float*>(p.xscale), const_cast<float*>(p.xsum), const_cast<float*>(p.xl1));
+  }
   // decode kernel: programmatic dependent launch after the preparation kernel, so that its weight
   // copies overlap the preparation; the kernel itself waits before it touches the prepared x
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.rw * p.bw * p.nchunks, pl.mtiles);
-  cfg.blockDim = dim3(kDT);
+  cfg.gridDim = dim3(p.rw * (p.bw / p.bpc) * p.nchunks, pl.mtiles);
+  cfg.blockDim = dim3(kDT * p.bpc);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = merged ? 0 : 1;
   if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
 }
