@@ -9,8 +9,9 @@ the 126 MB L2, so every step streams them from HBM again.
 
 value  = algorithmic bytes (packed bits + fp32 coefficients + x + y) per second, summed over
          all ranks, inputs resident in HBM, timed with CUDA events on the launching stream.
-e2e    = the same through module.forward with HOST activations: pinned x -> device copy,
-         forward, device -> pinned host copy of y, every layer, every step.
+e2e    = the same through module.bind_host (the C entry point bqq_forward_host) with HOST
+         activations: pinned x -> device copy, forward, device -> pinned host copy of y, every
+         layer, every step, one stream synchronisation per step.
 With N > 1 ranks (weak scaling) each rank owns one row-patch shard of layers N times as
 tall (its shard has the base shape) and every layer's outputs are all-gathered with NCCL.
 
@@ -219,6 +220,8 @@ def main():
         L._ensure_packed()
     torch.cuda.synchronize()
     step_bytes = sum(alg_bytes(o, i, bw) for (o, i, bw) in cfgs)
+    from bqq_b200 import _cabi
+    launches_per_step = sum(_cabi.lib.bqq_decode_launches(L._dims(), 1) for L in layers)
     gathers = [torch.empty(world, o, device=device, dtype=torch.bfloat16) for (o, i, bw) in cfgs] if world > 1 else None
 
     def step():
@@ -261,13 +264,18 @@ def main():
         xh = [x.cpu().pin_memory() for x in xs]
         yh = [torch.empty(1, o, dtype=torch.bfloat16).pin_memory() for (o, i, bw) in cfgs]
 
+        with torch.no_grad():
+            bound = [L.bind_host(xh[n], yh[n])[0] for n, L in enumerate(layers)] if world == 1 else None
+
         def e2e_step():
             with torch.no_grad():
                 for n, L in enumerate(layers):
-                    y = L(xh[n].to(device, non_blocking=True))
                     if world > 1:
+                        y = L(xh[n].to(device, non_blocking=True))
                         dist.all_gather_into_tensor(gathers[n].view(-1), y.view(-1))
-                    yh[n].copy_(y, non_blocking=True)
+                        yh[n].copy_(y, non_blocking=True)
+                    else:
+                        bound[n]()                        # one C call: copy in, kernels, copy out
             stream.synchronize()
 
         for _ in range(3):
@@ -309,7 +317,7 @@ def main():
                     'h2d_bytes_per_step': sum(i * 2 for (o, i, bw) in cfgs),
                     'd2h_bytes_per_step': sum(o * 2 for (o, i, bw) in cfgs),
                     'steps': e2e_steps, 'ms_per_step': e2e_ms / e2e_steps},
-            'gpu_launches': 2 * len(cfgs) * args.steps,      # activation preparation + decode kernel per layer
+            'gpu_launches': launches_per_step * args.steps,  # decode kernel (+ activation preparation kernel) per layer
             'roofline': {'bound': 'hbm', 'achieved': per_gpu, 'peak': peak, 'unit': 'GB/s',
                          'frac': per_gpu / peak, 'traffic': TRAFFIC_RATIO * step_bytes / len(cfgs),
                          'traffic_note': 'dram read+write bytes of one ncu capture (4096x14336, 4 bit layers: '

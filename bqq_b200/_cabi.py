@@ -23,6 +23,7 @@ EXPORTS = [
     'bqq_decode_workspace_bytes', 'bqq_forward_decode',
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
+    'bqq_decode_launches', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
     'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc',
 ]
 
@@ -63,6 +64,9 @@ def _load():
         'bqq_forward_prefill': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_forward': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_reconstruct_weight': (i32, [lp, vp, i32, f32, vp]),
+        'bqq_decode_launches': (i32, [dp, i32]),
+        'bqq_forward_host_workspace_bytes': (sz, [dp, i32, i32, i32]),
+        'bqq_forward_host': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_noalloc_scratch_bytes': (sz, []),
         'bqq_forward_decode_noalloc': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp]),
     }

@@ -189,6 +189,74 @@ class _BqqForwardMixin:
                       'bqq_forward_prefill')
         return y.reshape(*X.shape[:-1], out_f)
 
+    def bind_host(self, X_host, out=None):
+        """Prepare the forward for activations that live in HOST memory and return `(run, out)`.
+
+        `X_host` [..., in] is a CPU tensor (pinned for asynchronous copies), `out` [..., out] a CPU tensor
+        of X's dtype (pinned; allocated when None).  Each `run()` is one C call (bqq_forward_host) that
+        enqueues the host->device copy of X_host's current contents, the kernels and the device->host
+        copy into `out` on the stream that was current when bind_host was called; nothing is
+        synchronised: synchronise that stream before reading `out`.  The binding holds raw pointers: it
+        stays valid while X_host, out and the layer's parameters and buffers are not reallocated
+        (in-place updates are fine)."""
+        self._check_inference_only(X_host)
+        if X_host.is_cuda:
+            raise RuntimeError('bqq_b200: host forward expects a CPU tensor; use forward() for device tensors')
+        if X_host.dtype not in _DTYPE_CODE:
+            raise RuntimeError(f'bqq_b200: unsupported activation dtype {X_host.dtype} (fp32, bf16, fp16 only)')
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        in_f = self.col_width * self.z_col
+        out_f = self.row_width * self.y_row
+        if X_host.shape[-1] != in_f:
+            raise RuntimeError(f'bqq_b200: last dim of X is {X_host.shape[-1]}, layer expects {in_f}')
+        x2 = X_host.reshape(-1, in_f)
+        if x2.stride(-1) != 1 or x2.data_ptr() != X_host.data_ptr():
+            raise RuntimeError('bqq_b200: X_host must be viewable as [M, in_features] rows with unit inner stride')
+        M = x2.shape[0]
+        if out is None:
+            out = torch.empty((*X_host.shape[:-1], out_f), dtype=X_host.dtype, pin_memory=True)
+        y2 = out.reshape(-1, out_f)
+        if (out.is_cuda or out.dtype != X_host.dtype or y2.shape[0] != M or y2.stride(-1) != 1
+                or y2.data_ptr() != out.data_ptr()):
+            raise RuntimeError("bqq_b200: `out` must be a CPU tensor [..., out_features] of X's dtype with unit inner stride")
+        if M == 0:
+            return (lambda: out), out
+        code = _DTYPE_CODE[X_host.dtype]
+        layer = self._layer(st)
+        with torch.cuda.device(device):
+            nbytes = lib.bqq_forward_host_workspace_bytes(st.dims, M, code, code)
+            ws = _workspace(device, 'host_decode' if M <= _cabi.DECODE_MAX_M else 'host_prefill', nbytes)
+            stream = torch.cuda.current_stream(device).cuda_stream
+        args = (layer, x2.data_ptr(), code, M, x2.stride(0), y2.data_ptr(), code, y2.stride(0),
+                ws.data_ptr(), ws.numel(), stream)
+        call = lib.bqq_forward_host
+        index = device.index
+        keep = (x2, y2, ws, layer, st)                  # keeps the bound memory alive with the closure
+        result = out
+
+        def run():
+            if torch.cuda.current_device() != index:
+                with torch.cuda.device(index):
+                    rc = call(*args)
+            else:
+                rc = call(*args)
+            if rc:
+                check(rc, 'bqq_forward_host')
+            return result
+
+        return run, out
+
+    def forward_host(self, X_host, out=None):
+        """One-shot form of bind_host: enqueue the forward of host activations `X_host` into the host
+        tensor `out` (allocated pinned when None) and return `out`; synchronise the current stream of
+        the layer's GPU before reading it.  The values are those of forward(X_host.to(device)).cpu()."""
+        if not X_host.is_cuda and X_host.dim() >= 1 and X_host.stride(-1) != 1:
+            X_host = X_host.contiguous()
+        run, out = self.bind_host(X_host, out)
+        run()
+        return out
+
     def _weight_gpu(self, dtype):
         st = self._ensure_packed()
         device = st.zplanes.device

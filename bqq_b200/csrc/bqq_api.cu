@@ -100,6 +100,54 @@ int bqq_forward(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_
   return bqq_forward_prefill(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
 }
 
+int bqq_decode_launches(const BqqDims* dims, int M) {
+  if (int rc = check_dims(dims)) return rc;
+  if (M <= 0 || M > BQQ_DECODE_MAX_M) return BQQ_ERR_BAD_SHAPE;
+  return decode_launches(dims, M);
+}
+
+static inline size_t host_stage_bytes(size_t rows, size_t cols, int dtype) {
+  return (rows * cols * dtype_size(dtype) + 255) / 256 * 256;
+}
+
+size_t bqq_forward_host_workspace_bytes(const BqqDims* dims, int M, int x_dtype, int y_dtype) {
+  if (check_dims(dims) != BQQ_OK || M <= 0 || !dtype_size(x_dtype) || !dtype_size(y_dtype)) return 0;
+  const size_t inner = bqq_forward_workspace_bytes(dims, M);
+  if (!inner) return 0;
+  Geom g(*dims);
+  return inner + host_stage_bytes(M, g.in_features(), x_dtype) + host_stage_bytes(M, g.out_features(), y_dtype);
+}
+
+int bqq_forward_host(const BqqLayer* layer, const void* x_host, int x_dtype, int M, int64_t ldx, void* y_host,
+                     int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  rc = check_io(layer, x_host, x_dtype, M, ldx, y_host, y_dtype, ldy);
+  if (rc) return rc;
+  if (!workspace) return BQQ_ERR_WORKSPACE;
+  if ((uintptr_t)workspace & 255) return BQQ_ERR_MISALIGNED;
+  if (workspace_bytes < bqq_forward_host_workspace_bytes(&layer->dims, M, x_dtype, y_dtype)) return BQQ_ERR_WORKSPACE;
+  Geom g(layer->dims);
+  const size_t inner = bqq_forward_workspace_bytes(&layer->dims, M);
+  const size_t xs = dtype_size(x_dtype), ys = dtype_size(y_dtype);
+  char* xd = reinterpret_cast<char*>(workspace) + inner;
+  char* yd = xd + host_stage_bytes(M, g.in_features(), x_dtype);
+  cudaStream_t st = (cudaStream_t)stream;
+  // the forward's own workspace comes first so that its zero-initialised counters stay where they were
+  const size_t xrow = g.in_features() * xs, yrow = g.out_features() * ys;
+  cudaError_t ce = (M == 1 || ldx == g.in_features())
+                       ? cudaMemcpyAsync(xd, x_host, xrow * M, cudaMemcpyHostToDevice, st)
+                       : cudaMemcpy2DAsync(xd, xrow, x_host, ldx * xs, xrow, M, cudaMemcpyHostToDevice, st);
+  if (ce != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
+  rc = bqq_forward(layer, xd, x_dtype, M, g.in_features(), yd, y_dtype, g.out_features(), workspace, inner, stream);
+  if (rc) return rc;
+  ce = (M == 1 || ldy == g.out_features())
+           ? cudaMemcpyAsync(y_host, yd, yrow * M, cudaMemcpyDeviceToHost, st)
+           : cudaMemcpy2DAsync(y_host, ldy * ys, yd, yrow, yrow, M, cudaMemcpyDeviceToHost, st);
+  if (ce != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
+  return BQQ_OK;
+}
+
 int bqq_reconstruct_weight(const BqqLayer* layer, void* W, int w_dtype, float scale, void* stream) {
   int rc = check_layer(layer);
   if (rc) return rc;

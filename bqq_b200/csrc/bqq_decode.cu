@@ -48,6 +48,13 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
 
 size_t decode_counter_bytes() { return kCounterBytes; }
 
+int decode_launches(const BqqDims* dims, int M) {
+  Geom g(*dims);
+  DecodePlan pl = make_decode_plan(g, M);
+  if (pl.variant < 0) return BQQ_ERR_UNSUPPORTED;
+  return pl.bpc > 1 ? 1 : 2;
+}
+
 size_t decode_workspace_bytes(const BqqDims* dims, int M) {
   Geom g(*dims);
   DecodePlan pl = make_decode_plan(g, M);

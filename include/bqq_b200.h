@@ -170,6 +170,31 @@ int bqq_forward(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_
                 void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Number of kernels one bqq_forward_decode call enqueues for this layer shape and
+ * M (1 or 2: short single-chunk layers at M = 1 prepare x inside the decode
+ * kernel, all others launch a preparation kernel first); negative BQQ_ERR_* for
+ * bad arguments.  For launch accounting; the reference has no such query.
+ */
+int bqq_decode_launches(const BqqDims* dims, int M);
+
+/*
+ * bqq_forward with HOST activations and outputs: copies x [M, ldx] from host
+ * memory into the workspace, runs bqq_forward on the stream and copies y back to
+ * host memory, all asynchronously on `stream` (use pinned host buffers; with
+ * pageable memory the copies block the host).  It is what the reference module
+ * does when it is handed a CPU tensor (`X.to(self.Y.device)`,
+ * src/bqq_modules.py:35) without the per-call tensor allocations.  The caller
+ * synchronises the stream before reading y_host.  The workspace must hold
+ * bqq_forward_host_workspace_bytes (the forward's workspace first, then the two
+ * staging buffers), be 256-byte aligned and obey the decode workspace's
+ * zero-initialisation rule.
+ */
+size_t bqq_forward_host_workspace_bytes(const BqqDims* dims, int M, int x_dtype, int y_dtype);
+int bqq_forward_host(const BqqLayer* layer, const void* x_host, int x_dtype, int M, int64_t ldx,
+                     void* y_host, int y_dtype, int64_t ldy,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * bqq_forward_decode without a caller workspace (no counterpart in the reference,
  * whose extension allocates through torch on every call).  It is for callers that
  * cannot allocate device memory at the point of the call: operators hosted by a

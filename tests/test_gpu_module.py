@@ -116,3 +116,52 @@ def test_sharded_rows_equal_unsharded():
     for world in (2, 4, 8):
         parts = [_fwd(shard_rows(bq, r, world), X.cuda()) for r in range(world)]
         assert torch.equal(torch.cat(parts, dim=-1), full)
+
+
+@pytest.mark.parametrize('M,dtype', [(1, torch.bfloat16), (3, torch.float32), (40, torch.float16)])
+def test_forward_host_equals_device_forward(M, dtype):
+    """bqq_forward_host (host buffers in and out, one C call) gives the values of the device forward,
+    for the decode path (M <= 16) and the prefill path, also with a strided host input."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, _ = synth_layer(2, 6, 5, 32, 32, 32, 1, seed=21, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    g = torch.Generator().manual_seed(5)
+    wide = torch.randn(M, 5 * 32 + 8, generator=g).to(dtype).pin_memory()
+    xh = wide[:, :5 * 32]                                   # row stride larger than in_features
+    want = _fwd(bq, xh.cuda())
+    out = torch.empty(M, 6 * 32, dtype=dtype).pin_memory()
+    with torch.no_grad():
+        got = bq.forward_host(xh, out)
+        torch.cuda.current_stream().synchronize()
+        assert got is out and torch.equal(out.cuda(), want)
+        got2 = bq.forward_host(xh)                          # allocates a pinned output
+        torch.cuda.current_stream().synchronize()
+        assert got2.is_pinned() and torch.equal(got2.cuda(), want)
+        with pytest.raises(RuntimeError, match='CPU tensor'):
+            bq.forward_host(xh.cuda())
+
+
+def test_decode_launch_count():
+    """Short single-chunk layers at batch 1 take one kernel, everything else two."""
+    from bqq_b200 import _cabi
+    lib = _cabi.lib
+    assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 32, 32, 32), 1) == 1
+    assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 32, 32, 32), 4) == 2
+    assert lib.bqq_decode_launches(_cabi.dims(2, 128, 448, 32, 32, 32), 1) == 2
+    assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 64, 64, 32), 1) == 2
+    assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 32, 32, 32), 17) < 0
+
+
+def test_bind_host_reads_current_contents():
+    """A host binding is one C call per run and sees in-place changes of its input buffer."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(2, 4, 4, 32, 32, 32, 1, seed=22, bias=False)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    xh = X.to(torch.bfloat16).pin_memory()
+    with torch.no_grad():
+        run, out = bq.bind_host(xh)
+        for scale in (1.0, -0.5):
+            xh.copy_((X * scale).to(torch.bfloat16))
+            assert run() is out
+            torch.cuda.current_stream().synchronize()
+            assert torch.equal(out.cuda(), _fwd(bq, xh.cuda()))
