@@ -13,7 +13,9 @@ e2e    = the same through module.bind_host (the C entry point bqq_forward_host) 
          activations: pinned x -> device copy, forward, device -> pinned host copy of y, every
          layer, every step, one stream synchronisation per step.
 With N > 1 ranks (weak scaling) each rank owns one row-patch shard of layers N times as
-tall (its shard has the base shape) and every layer's outputs are all-gathered with NCCL.
+tall (its shard has the base shape) and every layer's outputs are gathered on all ranks by the
+library's peer-to-peer store kernel (bqq_peer_gather; NCCL only carries the set-up and the timing
+reduction).
 
 `--impl reference` times the CPU port of the reference algorithm (oracle/bqq_oracle.c,
 dense-weight rebuild + matmul, all host threads) on the same 12 layers.
@@ -169,9 +171,9 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def shutdown(world, graphs):
-    """Release captured graphs before the NCCL communicator goes away (a communicator whose
-    collectives live in a CUDA graph can block in destroy), and never let teardown hang the job."""
+def shutdown(world, graphs, peer=None):
+    """Release captured graphs and the peer gather buffers before the communicator goes away, and
+    never let teardown hang the job."""
     import torch
     import torch.distributed as dist
     for g in graphs:
@@ -181,6 +183,9 @@ def shutdown(world, graphs):
         timer = threading.Timer(30.0, lambda: os._exit(0))
         timer.daemon = True
         timer.start()
+        if peer is not None:
+            peer.status()              # raises if a bounded wait on a peer gave up during the run
+            peer.close()
         dist.barrier()
         dist.destroy_process_group()
         timer.cancel()
@@ -222,14 +227,18 @@ def main():
     step_bytes = sum(alg_bytes(o, i, bw) for (o, i, bw) in cfgs)
     from bqq_b200 import _cabi
     launches_per_step = sum(_cabi.lib.bqq_decode_launches(L._dims(), 1) for L in layers)
-    gathers = [torch.empty(world, o, device=device, dtype=torch.bfloat16) for (o, i, bw) in cfgs] if world > 1 else None
+    gathers = [torch.empty(1, world * o, device=device, dtype=torch.bfloat16) for (o, i, bw) in cfgs] if world > 1 else None
+    peer = None
+    if world > 1:
+        from bqq_b200.peer import PeerGatherGroup
+        peer = PeerGatherGroup(max(world * o * 2 for (o, i, bw) in cfgs), device)
 
     def step():
         with torch.no_grad():
             for n, (L, x) in enumerate(zip(layers, xs)):
                 y = L(x)
                 if world > 1:
-                    dist.all_gather_into_tensor(gathers[n].view(-1), y.view(-1))
+                    peer.gather(y, out=gathers[n])     # peer-to-peer stores, one kernel per rank
 
     stream = torch.cuda.Stream(device)
     with torch.cuda.stream(stream):
@@ -272,7 +281,7 @@ def main():
                 for n, L in enumerate(layers):
                     if world > 1:
                         y = L(xh[n].to(device, non_blocking=True))
-                        dist.all_gather_into_tensor(gathers[n].view(-1), y.view(-1))
+                        peer.gather(y, out=gathers[n])
                         yh[n].copy_(y, non_blocking=True)
                     else:
                         bound[n]()                        # one C call: copy in, kernels, copy out
@@ -297,7 +306,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
 
-    shutdown(world, [graph])          # communicator torn down before rank 0 spends time on the CPU baseline
+    shutdown(world, [graph], peer)          # communicator torn down before rank 0 spends time on the CPU baseline
     if rank == 0:
         peak, peak_kind = peaks()
         total_bytes = step_bytes * world
@@ -312,12 +321,13 @@ def main():
             'config': {'workload': 'decode_sweep_b1', 'layers': len(cfgs), 'P': P, 'Q': Q, 'r': R,
                        'activations': 'bf16', 'batch': 1, 'bytes_per_step_per_gpu': step_bytes,
                        'l2': 'working set per step (208.5 MB of packed planes) exceeds the 126 MB L2',
-                       'parallelism': f'row-patch shards x{world}, NCCL all-gather of outputs' if world > 1 else 'single GPU'},
+                       'parallelism': f'row-patch shards x{world}, outputs gathered by peer-to-peer stores (bqq_peer_gather)' if world > 1 else 'single GPU'},
             'e2e': {'value': e2e_val, 'unit': 'GB/s',
                     'h2d_bytes_per_step': sum(i * 2 for (o, i, bw) in cfgs),
                     'd2h_bytes_per_step': sum(o * 2 for (o, i, bw) in cfgs),
                     'steps': e2e_steps, 'ms_per_step': e2e_ms / e2e_steps},
-            'gpu_launches': launches_per_step * args.steps,  # decode kernel (+ activation preparation kernel) per layer
+            # decode kernel (+ activation preparation kernel) per layer, + the gather kernel when sharded
+            'gpu_launches': (launches_per_step + (len(cfgs) if world > 1 else 0)) * args.steps,
             'roofline': {'bound': 'hbm', 'achieved': per_gpu, 'peak': peak, 'unit': 'GB/s',
                          'frac': per_gpu / peak, 'traffic': TRAFFIC_RATIO * step_bytes / len(cfgs),
                          'traffic_note': 'dram read+write bytes of one ncu capture (4096x14336, 4 bit layers: '

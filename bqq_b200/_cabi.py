@@ -25,6 +25,8 @@ EXPORTS = [
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
     'bqq_decode_launches', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
     'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc',
+    'bqq_peer_region_bytes', 'bqq_peer_alloc', 'bqq_peer_open', 'bqq_peer_close', 'bqq_peer_free',
+    'bqq_peer_gather', 'bqq_peer_status',
 ]
 
 
@@ -36,6 +38,15 @@ class BqqLayer(C.Structure):
     _fields_ = [('dims', BqqDims), ('zplanes', C.c_void_p), ('yplanes', C.c_void_p),
                 ('a', C.c_void_p), ('b', C.c_void_p), ('c', C.c_void_p), ('d', C.c_void_p),
                 ('bias', C.c_void_p), ('coef_dtype', C.c_int32), ('bias_dtype', C.c_int32)]
+
+
+MAX_PEERS = 8
+PEER_HANDLE_BYTES = 64
+
+
+class BqqPeerGroup(C.Structure):
+    _fields_ = [('rank', C.c_int32), ('world', C.c_int32), ('regions', C.c_void_p * MAX_PEERS),
+                ('gather_bytes', C.c_uint64)]
 
 
 def _load():
@@ -67,6 +78,13 @@ def _load():
         'bqq_decode_launches': (i32, [dp, i32]),
         'bqq_forward_host_workspace_bytes': (sz, [dp, i32, i32, i32]),
         'bqq_forward_host': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
+        'bqq_peer_region_bytes': (sz, [sz]),
+        'bqq_peer_alloc': (i32, [sz, C.POINTER(vp), C.c_char_p]),
+        'bqq_peer_open': (i32, [C.c_char_p, C.POINTER(vp)]),
+        'bqq_peer_close': (i32, [vp]),
+        'bqq_peer_free': (i32, [vp]),
+        'bqq_peer_gather': (i32, [C.POINTER(BqqPeerGroup), vp, i32, i32, i64, i64, vp, i64, vp]),
+        'bqq_peer_status': (i32, [C.POINTER(BqqPeerGroup), vp]),
         'bqq_noalloc_scratch_bytes': (sz, []),
         'bqq_forward_decode_noalloc': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp]),
     }

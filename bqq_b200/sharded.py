@@ -23,10 +23,15 @@ def row_patch_range(row_width: int, rank: int, world: int):
     return rank * per, (rank + 1) * per
 
 
-def gather_columns(y_local: torch.Tensor, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+def gather_columns(y_local: torch.Tensor, group=None, out: torch.Tensor | None = None, peer=None) -> torch.Tensor:
     """All-gather column shards: y_local [..., n] on every rank -> [..., world*n], rank-major.
 
-    `out`, if given, is a reusable [world, rows, n] buffer (same dtype/device)."""
+    With `peer` (a bqq_b200.peer.PeerGatherGroup of the same ranks) the gather is one kernel of this
+    library that stores the slice into the peers' buffers over NVLink; otherwise it is the process
+    group's all_gather_into_tensor, for which `out`, if given, is a reusable [world, rows, n] buffer
+    (same dtype/device)."""
+    if peer is not None:
+        return peer.gather(y_local)
     world = dist.get_world_size(group)
     lead, n = y_local.shape[:-1], y_local.shape[-1]
     flat = y_local.reshape(-1, n).contiguous()
@@ -43,9 +48,9 @@ class ColumnParallelBinaryQuadratic(nn.Module):
     (gather=True) or only this rank's columns (gather=False, for consumers that are sharded
     the same way, e.g. attention heads or the SwiGLU product)."""
 
-    def __init__(self, full: BinaryQuadratic, rank: int, world: int, group=None, gather: bool = True):
+    def __init__(self, full: BinaryQuadratic, rank: int, world: int, group=None, gather: bool = True, peer=None):
         super().__init__()
-        self.rank, self.world, self.group, self.gather = rank, world, group, gather
+        self.rank, self.world, self.group, self.gather, self.peer = rank, world, group, gather, peer
         self.out_features = full.row_width * full.y_row
         self.shard = shard_rows(full, rank, world)
 
@@ -53,4 +58,4 @@ class ColumnParallelBinaryQuadratic(nn.Module):
         y = self.shard(X)
         if not self.gather or self.world == 1:
             return y
-        return gather_columns(y, self.group)
+        return gather_columns(y, self.group, peer=self.peer)

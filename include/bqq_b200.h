@@ -3,8 +3,8 @@
  *
  * Plain C: pointers and sizes only, no C++ or torch types.  Unless a function
  * says "host", every data pointer is a DEVICE pointer owned by the caller; the
- * library keeps no pointer after a call returns and never allocates or frees
- * device memory.  Work is enqueued on the CUDA stream passed as `stream`
+ * library keeps no pointer after a call returns and, apart from the explicit
+ * bqq_peer_alloc / bqq_peer_free pair, never allocates or frees device memory.  Work is enqueued on the CUDA stream passed as `stream`
  * (a cudaStream_t cast to void*; NULL = the legacy default stream).
  *
  * Every function returning int returns BQQ_OK (0) or a negative BQQ_ERR_*;
@@ -214,6 +214,46 @@ int bqq_forward_host(const BqqLayer* layer, const void* x_host, int x_dtype, int
 size_t bqq_noalloc_scratch_bytes(void);
 int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
                                void* y, int y_dtype, int64_t ldy, void* stream);
+
+/*
+ * Column gather for row-patch sharded layers by peer-to-peer stores (one process
+ * per GPU, all on one node).  The reference has no multi-GPU path; this replaces
+ * the all-gather a column-parallel wrapper of its module would issue.
+ *
+ * Set-up (the only calls of this library that allocate): every rank calls
+ * bqq_peer_alloc for its own region (control words + one gather buffer of
+ * `gather_bytes`), sends the 64-byte handle to its peers by any host channel,
+ * opens theirs with bqq_peer_open, and fills a BqqPeerGroup with the region
+ * pointers in rank order (its own allocation at [rank]).  All ranks must finish
+ * this before the first gather.  Tear-down: synchronise all ranks, bqq_peer_close
+ * the peers' regions, bqq_peer_free the own one.
+ *
+ * bqq_peer_gather: rank g passes its slice y_local [rows, n_local] (row pitch ldy
+ * elements); one kernel stores it into every rank's buffer, waits for all slices
+ * to arrive in the own buffer and copies the rows [rows, world*n_local] (rank-major
+ * columns, i.e. the unsharded column order) to `gathered` (row pitch ld_gathered).
+ * Every rank must issue the same sequence of gathers on the same group.  Waits on
+ * peers are bounded (about one second); if one gives up the kernel still ends and
+ * bqq_peer_status (which synchronises `stream`) returns BQQ_ERR_TIMEOUT.  No
+ * reduction is involved, so the gathered rows equal the single-GPU output bit for
+ * bit.  The call can be captured in a CUDA graph.
+ */
+#define BQQ_MAX_PEERS 8
+#define BQQ_PEER_HANDLE_BYTES 64
+typedef struct BqqPeerGroup {
+  int32_t rank, world;
+  void* regions[BQQ_MAX_PEERS];   /* every rank's region as mapped in this process */
+  uint64_t gather_bytes;          /* capacity of one gather buffer */
+} BqqPeerGroup;
+
+size_t bqq_peer_region_bytes(size_t gather_bytes);
+int bqq_peer_alloc(size_t gather_bytes, void** region, unsigned char handle[BQQ_PEER_HANDLE_BYTES]);
+int bqq_peer_open(const unsigned char handle[BQQ_PEER_HANDLE_BYTES], void** region);
+int bqq_peer_close(void* region);
+int bqq_peer_free(void* region);
+int bqq_peer_gather(const BqqPeerGroup* group, const void* y_local, int dtype, int rows, int64_t n_local,
+                    int64_t ldy, void* gathered, int64_t ld_gathered, void* stream);
+int bqq_peer_status(const BqqPeerGroup* group, void* stream);
 
 /*
  * Dense weight W [rw*P, cw*Q] row-major in element type w_dtype: the value of

@@ -1,0 +1,92 @@
+"""GPU: the peer-to-peer column gather (bqq_peer_gather).  A one-rank group runs the whole protocol
+(own flags and acknowledgements) on a single GPU; with two or more GPUs a two-process run checks the
+gathered values against every rank's slice, repeated gathers, and CUDA-graph replay."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _slice(rank, step, rows, n, dtype):
+    g = torch.Generator().manual_seed(1000 * step + rank)
+    return torch.randn(rows, n, generator=g).to(dtype)
+
+
+def _worker(rank, world, port, result_dir):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)      # host channel for the handles only
+    try:
+        from bqq_b200.peer import PeerGatherGroup
+        dev = torch.device('cuda', rank)
+        torch.cuda.set_device(dev)
+        grp = PeerGatherGroup(16 * world * 1024 * 4, dev)
+        step = 0
+        for rows, n, dtype in [(1, 512, torch.bfloat16), (4, 1024, torch.float32), (3, 130, torch.float16),
+                               (16, 1024, torch.bfloat16)]:
+            for _ in range(3):                                        # back-to-back gathers reuse the buffers
+                step += 1
+                y = _slice(rank, step, rows, n, dtype).to(dev)
+                got = grp.gather(y)
+                want = torch.cat([_slice(q, step, rows, n, dtype) for q in range(world)], dim=-1)
+                assert torch.equal(got.cpu(), want), (rank, step)
+        # strided input, leading dims, caller-provided output
+        step += 1
+        wide = torch.zeros(2, 3, 96, dtype=torch.bfloat16, device=dev)
+        wide[..., :64] = _slice(rank, step, 6, 64, torch.bfloat16).view(2, 3, 64).to(dev)
+        out = torch.empty(6, world * 64, dtype=torch.bfloat16, device=dev)
+        got = grp.gather(wide[..., :64], out=out)
+        want = torch.cat([_slice(q, step, 6, 64, torch.bfloat16) for q in range(world)], dim=-1).view(2, 3, -1)
+        assert got.data_ptr() == out.data_ptr() and torch.equal(got.cpu(), want)
+        # graph capture and replay: the sequence number lives on the device
+        y = torch.zeros(1, 256, dtype=torch.bfloat16, device=dev)
+        out = torch.empty(1, world * 256, dtype=torch.bfloat16, device=dev)
+        st = torch.cuda.Stream(dev)
+        with torch.cuda.stream(st):
+            grp.gather(y, out=out)
+            st.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=st):
+                grp.gather(y, out=out)
+            for rep in range(4):
+                step += 1
+                y.copy_(_slice(rank, step, 1, 256, torch.bfloat16))
+                graph.replay()
+                st.synchronize()
+                want = torch.cat([_slice(q, step, 1, 256, torch.bfloat16) for q in range(world)], dim=-1)
+                assert torch.equal(out.cpu(), want), (rank, 'replay', rep)
+            graph.reset()
+            grp.status()
+        grp.close()
+        with open(os.path.join(result_dir, f'ok{rank}'), 'w') as f:
+            f.write('ok')
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, tmp_path):
+    mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True,
+                       start_method='spawn')
+    assert all((tmp_path / f'ok{r}').exists() for r in range(world))
+
+
+def test_peer_gather_single_rank(tmp_path):
+    _run(1, tmp_path)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+def test_peer_gather_two_ranks(tmp_path):
+    _run(2, tmp_path)
