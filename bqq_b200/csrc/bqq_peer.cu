@@ -2,17 +2,19 @@
 //
 // A column-parallel BinaryQuadratic layer leaves rank g with the output columns
 // [g*n, (g+1)*n) of every row.  Each rank owns one region (cudaMalloc + CUDA IPC, mapped by
-// all peers): control words and one gather buffer [rows][world*n].  A gather is one kernel
-// per rank:
-//   1. wait until every peer has acknowledged the previous gather (my old data is consumed),
-//   2. store my column slice into every rank's buffer (NVLink stores, 16 bytes per thread),
-//      fence, then publish the gather's sequence number in each peer's flag word for me,
-//   3. wait until every rank's flag word in MY region carries the sequence number,
-//   4. copy the complete rows out of my buffer into the caller's tensor and acknowledge to
-//      every peer.
-// Every wait is bounded by a clock budget; when one gives up the kernel still finishes, the
-// status word is set and the next bqq_peer_status call reports BQQ_ERR_TIMEOUT.  The sequence
-// number lives on the device, so a captured CUDA graph can replay the gather.
+// all peers): control words and two halves of 8-byte slots, one slot per 32-bit word of the
+// gathered rows [rows][world*n].  A gather is one kernel per rank:
+//   send: every 32-bit word of my slice goes, together with the gather's sequence number, as one
+//         8-byte store into the matching slot of every rank's region (NVLink stores; an 8-byte
+//         store is indivisible, so no fence or separate flag is needed);
+//   receive: every slot of my own region is polled until it carries the sequence number, and its
+//         data word is written to the caller's tensor.
+// Consecutive gathers alternate between the two halves.  A rank can only start gather e+2 after it
+// has received gather e+1 from every peer, which the peers send after their gather e has returned,
+// so a half is never overwritten while its owner still reads it.
+// Every poll is bounded by a clock budget; when one gives up the kernel still finishes, the status
+// word is set and the next bqq_peer_status call reports BQQ_ERR_TIMEOUT.  The sequence number lives
+// on the device, so a captured CUDA graph can replay the gather.
 #include <cuda_runtime.h>
 #include <string.h>
 
@@ -20,108 +22,77 @@
 
 namespace bqq {
 
-constexpr size_t kPeerCtrlBytes = 512;         // epoch, status, counters | flags | acks
-constexpr int kFlagWord = 32;                  // word offset of flags[world] inside the region
-constexpr int kAckWord = 64;                   // word offset of acks[world]
-constexpr long long kPeerWaitBudget = 2000000000LL;   // clock cycles (~1 s) before a wait gives up
+constexpr size_t kPeerCtrlBytes = 512;         // sequence number, status, block counter
+constexpr long long kPeerWaitBudget = 2000000000LL;   // clock cycles (~1 s) before a poll gives up
 constexpr int kPeerThreads = 256;
-constexpr int kPeerMaxBlocks = 32;             // far below the number of SMs: all blocks are co-resident
+constexpr int kPeerMaxBlocks = 32;
 
 struct PeerArgs {
   uint8_t* regions[BQQ_MAX_PEERS];             // every rank's region as mapped in this process
-  const uint8_t* src;                          // local slice [rows][ld_src] bytes
-  uint8_t* out;                                // gathered rows [rows][ld_out] bytes (local), may be NULL
+  const uint32_t* src;                         // local slice, rows of `row_words` words, pitch ld_src words
+  uint32_t* out;                               // gathered rows, pitch ld_out words
   int rank, world, rows;
-  long long row_bytes;                         // bytes of one row of the local slice (n * element size)
-  long long ld_src, ld_out;                    // row pitches in bytes
+  int row_words;                               // 32-bit words of one row of the local slice
+  long long ld_src, ld_out;                    // row pitches in words
+  unsigned long long half_bytes;               // bytes of one half of the slot area
 };
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ void st_slot(uint2* p, uint32_t data, uint32_t seq) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Bounded wait until *p has reached `target` (sequence numbers wrap).
-__device__ __forceinline__ bool wait_reached(const unsigned* p, unsigned target) {
-  if ((int)(ld_acquire_sys(p) - target) >= 0) return true;
-  const long long t0 = clock64();
-  while ((int)(ld_acquire_sys(p) - target) < 0) {
-    if (clock64() - t0 > kPeerWaitBudget) return false;
-    __nanosleep(64);
-  }
-  return true;
-}
-
-// Loads bypass L1 (the source may have been written by another GPU since this SM last read it).
-__device__ __forceinline__ void copy_rows(uint8_t* dst, long long ld_dst, const uint8_t* src, long long ld_src,
-                                          int rows, long long row_bytes, int tid, int nthreads) {
-  const bool vec = ((row_bytes | ld_dst | ld_src | (long long)(uintptr_t)dst | (long long)(uintptr_t)src) & 15) == 0;
-  if (vec) {
-    const long long per_row = row_bytes >> 4, total = per_row * rows;
-    for (long long e = tid; e < total; e += nthreads) {
-      const long long r = e / per_row, c = e - r * per_row;
-      reinterpret_cast<uint4*>(dst + r * ld_dst)[c] = __ldcg(reinterpret_cast<const uint4*>(src + r * ld_src) + c);
-    }
-  } else {
-    const long long per_row = row_bytes >> 1, total = per_row * rows;      // every element type is >= 2 bytes
-    for (long long e = tid; e < total; e += nthreads) {
-      const long long r = e / per_row, c = e - r * per_row;
-      reinterpret_cast<uint16_t*>(dst + r * ld_dst)[c] = __ldcg(reinterpret_cast<const uint16_t*>(src + r * ld_src) + c);
-    }
-  }
 }
 
 __global__ void __launch_bounds__(kPeerThreads)
 bqq_peer_gather_kernel(const PeerArgs a) {
-  __shared__ int s_last, s_fail;
+  __shared__ int s_giveup;
   unsigned* mine = reinterpret_cast<unsigned*>(a.regions[a.rank]);
   const int tid = threadIdx.x;
-  const int gtid = blockIdx.x * kPeerThreads + tid, gthreads = gridDim.x * kPeerThreads;
-  const unsigned e = *reinterpret_cast<volatile unsigned*>(mine) + 1u;    // sequence number of this gather
-  const long long gathered_row = a.row_bytes * a.world;
-  if (tid == 0) s_fail = 0;
+  const long long gtid = (long long)blockIdx.x * kPeerThreads + tid, gthreads = (long long)gridDim.x * kPeerThreads;
+  const unsigned count = *reinterpret_cast<volatile unsigned*>(mine) + 1u;   // gathers on this group so far
+  const unsigned e = count | 0x80000000u;             // sequence number: never the zero of a fresh slot
+  const unsigned long long half = (count & 1u) * a.half_bytes;
+  const long long grow = (long long)a.row_words * a.world;                // words of one gathered row
+  if (tid == 0) s_giveup = 0;
   __syncthreads();
 
-  // 1. every peer has consumed what I stored for the previous gather
-  if (tid < a.world && !wait_reached(mine + kAckWord + tid, e - 1u)) s_fail = 1;
-  __syncthreads();
-
-  // 2. my slice into every rank's buffer, then publish
-  for (int q = 0; q < a.world; ++q)
-    copy_rows(a.regions[q] + kPeerCtrlBytes + a.rank * a.row_bytes, gathered_row, a.src, a.ld_src, a.rows,
-              a.row_bytes, gtid, gthreads);
-  __threadfence_system();
-  __syncthreads();
-  if (tid == 0) s_last = atomicAdd(mine + 2, 1u) == gridDim.x - 1;
-  __syncthreads();
-  if (s_last) {
-    __threadfence_system();
-    if (tid < a.world) st_release_sys(reinterpret_cast<unsigned*>(a.regions[tid]) + kFlagWord + a.rank, e);
-    if (tid == 0) mine[2] = 0u;
+  // send: my words into everybody's slots (my own included)
+  const long long nsend = (long long)a.rows * a.row_words;
+  for (long long w = gtid; w < nsend; w += gthreads) {
+    const long long r = w / a.row_words, c = w - r * a.row_words;
+    const uint32_t data = a.src[r * a.ld_src + c];
+    const long long slot = r * grow + (long long)a.rank * a.row_words + c;
+    for (int q = 0; q < a.world; ++q)
+      st_slot(reinterpret_cast<uint2*>(a.regions[q] + kPeerCtrlBytes + half) + slot, data, e);
   }
 
-  // 3. every rank's slice has arrived in my buffer
-  if (tid < a.world && !wait_reached(mine + kFlagWord + tid, e)) s_fail = 1;
-  __syncthreads();
-
-  // 4. copy the rows out and acknowledge
-  if (a.out)
-    copy_rows(a.out, a.ld_out, reinterpret_cast<const uint8_t*>(mine) + kPeerCtrlBytes, gathered_row, a.rows,
-              gathered_row, gtid, gthreads);
-  if (s_fail && tid == 0) atomicExch(mine + 1, 1u);
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) s_last = atomicAdd(mine + 3, 1u) == gridDim.x - 1;
-  __syncthreads();
-  if (s_last) {
-    if (tid < a.world) st_release_sys(reinterpret_cast<unsigned*>(a.regions[tid]) + kAckWord + a.rank, e);
-    if (tid == 0) {
-      mine[3] = 0u;
-      *reinterpret_cast<volatile unsigned*>(mine) = e;
+  // receive: poll every slot of my region
+  const uint2* slots = reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(mine) + kPeerCtrlBytes + half);
+  const long long nrecv = (long long)a.rows * grow;
+  for (long long w = gtid; w < nrecv; w += gthreads) {
+    uint2 v = ld_slot(slots + w);
+    if (v.y != e) {
+      const long long t0 = clock64();
+      while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
+        if (clock64() - t0 > kPeerWaitBudget) { s_giveup = 1; break; }
+        __nanosleep(32);
+        v = ld_slot(slots + w);
+      }
     }
+    const long long r = w / grow, c = w - r * grow;
+    a.out[r * a.ld_out + c] = v.x;
+  }
+  __syncthreads();
+  if (s_giveup && tid == 0) atomicExch(mine + 1, 1u);
+
+  // the last block to finish advances the sequence number (every block has read it by then)
+  __threadfence();
+  if (tid == 0 && atomicAdd(mine + 2, 1u) == gridDim.x - 1) {
+    mine[2] = 0u;
+    *reinterpret_cast<volatile unsigned*>(mine) = count;
   }
 }
 
@@ -131,7 +102,9 @@ using namespace bqq;
 
 extern "C" {
 
-size_t bqq_peer_region_bytes(size_t gather_bytes) { return kPeerCtrlBytes + (gather_bytes + 255) / 256 * 256; }
+// control words + two halves of 8-byte slots (one per 32-bit word of the largest gathered result)
+static inline size_t peer_half_bytes(size_t gather_bytes) { return (2 * gather_bytes + 255) / 256 * 256; }
+size_t bqq_peer_region_bytes(size_t gather_bytes) { return kPeerCtrlBytes + 2 * peer_half_bytes(gather_bytes); }
 
 int bqq_peer_alloc(size_t gather_bytes, void** region, unsigned char handle[BQQ_PEER_HANDLE_BYTES]) {
   if (!region || !handle) return BQQ_ERR_NULL;
@@ -178,21 +151,26 @@ int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int r
   if (g->world < 1 || g->world > BQQ_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return BQQ_ERR_BAD_SHAPE;
   const size_t es = dtype_size(dtype);
   if (!es) return BQQ_ERR_DTYPE;
-  if (rows <= 0 || n_local <= 0 || ldy < n_local || (gathered && ld_gathered < n_local * g->world)) return BQQ_ERR_BAD_SHAPE;
+  if (!gathered) return BQQ_ERR_NULL;
+  if (rows <= 0 || n_local <= 0 || ldy < n_local || ld_gathered < n_local * g->world) return BQQ_ERR_BAD_SHAPE;
   if ((size_t)rows * n_local * g->world * es > g->gather_bytes) return BQQ_ERR_WORKSPACE;
+  if (((size_t)n_local * es) % 4 || ((size_t)ldy * es) % 4 || ((size_t)ld_gathered * es) % 4 ||
+      ((uintptr_t)y_local & 3) || ((uintptr_t)gathered & 3))
+    return BQQ_ERR_MISALIGNED;                                  // slices travel as 32-bit words
   PeerArgs a;
   for (int q = 0; q < g->world; ++q) {
     if (!g->regions[q]) return BQQ_ERR_NULL;
     a.regions[q] = reinterpret_cast<uint8_t*>(g->regions[q]);
   }
-  a.src = reinterpret_cast<const uint8_t*>(y_local);
-  a.out = reinterpret_cast<uint8_t*>(gathered);
+  a.src = reinterpret_cast<const uint32_t*>(y_local);
+  a.out = reinterpret_cast<uint32_t*>(gathered);
   a.rank = g->rank; a.world = g->world; a.rows = rows;
-  a.row_bytes = (long long)n_local * es;
-  a.ld_src = (long long)ldy * es;
-  a.ld_out = (long long)ld_gathered * es;
-  const long long vec = ((long long)rows * a.row_bytes * g->world + 15) / 16;
-  int blocks = (int)((vec + 4 * kPeerThreads - 1) / (4 * kPeerThreads));
+  a.row_words = (int)((size_t)n_local * es / 4);
+  a.ld_src = (long long)((size_t)ldy * es / 4);
+  a.ld_out = (long long)((size_t)ld_gathered * es / 4);
+  a.half_bytes = peer_half_bytes(g->gather_bytes);
+  const long long words = (long long)rows * a.row_words * g->world;
+  int blocks = (int)((words + 2 * kPeerThreads - 1) / (2 * kPeerThreads));
   blocks = blocks < 1 ? 1 : (blocks > kPeerMaxBlocks ? kPeerMaxBlocks : blocks);
   bqq_peer_gather_kernel<<<blocks, kPeerThreads, 0, (cudaStream_t)stream>>>(a);
   return launch_status();

@@ -221,17 +221,19 @@ int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype
  * the all-gather a column-parallel wrapper of its module would issue.
  *
  * Set-up (the only calls of this library that allocate): every rank calls
- * bqq_peer_alloc for its own region (control words + one gather buffer of
- * `gather_bytes`), sends the 64-byte handle to its peers by any host channel,
+ * bqq_peer_alloc for its own region (control words + slots for gathered results
+ * of up to `gather_bytes`; bqq_peer_region_bytes in all), sends the 64-byte handle to its peers by any host channel,
  * opens theirs with bqq_peer_open, and fills a BqqPeerGroup with the region
  * pointers in rank order (its own allocation at [rank]).  All ranks must finish
  * this before the first gather.  Tear-down: synchronise all ranks, bqq_peer_close
  * the peers' regions, bqq_peer_free the own one.
  *
  * bqq_peer_gather: rank g passes its slice y_local [rows, n_local] (row pitch ldy
- * elements); one kernel stores it into every rank's buffer, waits for all slices
- * to arrive in the own buffer and copies the rows [rows, world*n_local] (rank-major
+ * elements); one kernel stores it into every rank's region, waits for all slices
+ * to arrive in the own region and writes the rows [rows, world*n_local] (rank-major
  * columns, i.e. the unsharded column order) to `gathered` (row pitch ld_gathered).
+ * Slices travel as 32-bit words: n_local, ldy and ld_gathered times the element
+ * size must be multiples of 4 bytes (BQQ_ERR_MISALIGNED otherwise).
  * Every rank must issue the same sequence of gathers on the same group.  Waits on
  * peers are bounded (about one second); if one gives up the kernel still ends and
  * bqq_peer_status (which synchronises `stream`) returns BQQ_ERR_TIMEOUT.  No
@@ -243,7 +245,7 @@ int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype
 typedef struct BqqPeerGroup {
   int32_t rank, world;
   void* regions[BQQ_MAX_PEERS];   /* every rank's region as mapped in this process */
-  uint64_t gather_bytes;          /* capacity of one gather buffer */
+  uint64_t gather_bytes;          /* largest gathered result, as given to bqq_peer_alloc */
 } BqqPeerGroup;
 
 size_t bqq_peer_region_bytes(size_t gather_bytes);
