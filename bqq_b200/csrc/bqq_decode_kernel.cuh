@@ -201,8 +201,11 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
                  uint8_t* __restrict__ xdig, float* __restrict__ xscale, float* __restrict__ xsum,
                  float* __restrict__ xl1) {
   // the decode kernel of this layer may start now: it first streams its weight planes and only
-  // then waits (griddepcontrol.wait) for this grid to finish
+  // then waits (griddepcontrol.wait) for this grid to finish.  This grid itself may have been
+  // started before the preceding kernel of the stream finished: wait for it before reading x or
+  // writing the workspace.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int pairs = Mp * cwp;
   const int pair = (blockIdx.x * 128 + threadIdx.x) >> 3;
   const bool inside = pair < pairs;
@@ -306,7 +309,9 @@ bqq_decode_kernel(const DecodeParams p) {
   const uint4* xres = reinterpret_cast<const uint4*>(sm + L.xres);      // MB only
   const float* xstat = reinterpret_cast<const float*>(sm + L.xstat);    // MB only
   if (MB) {
-    // this CTA prepares x itself (no preparation kernel was launched): every 8 lanes take one col patch
+    // this CTA prepares x itself (no preparation kernel was launched): every 8 lanes take one col patch.
+    // x and the workspace belong to earlier kernels of the stream until they have finished.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float* st = const_cast<float*>(xstat);
     for (int pair = tid >> 3; pair < nsg * kGroup; pair += (kDT * bpc) >> 3)
       xprep_pair<QT>(p.x, p.x_dtype, p.ldx, p.Q, NB, nsg, true, pair < p.cw && m0 < p.M, m0, pair, 0, 0, tid & 7,
@@ -561,6 +566,11 @@ bqq_decode_kernel(const DecodeParams p) {
   cp_async_wait<0>();
 
   if (!ok && lane == 0) atomicExch(p.counters + (kMaxCounters - 1), 1u);   // a bounded wait gave up
+  // The weights are consumed: the next kernel of the stream may become resident now (programmatic
+  // dependent launch; it starts once every CTA of this grid has got here).  A following kernel of this
+  // library prefetches its weights meanwhile and waits for this grid to finish before it touches
+  // anything else.  Triggering earlier would park the whole next grid on the SMs while this one runs.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ---- warp epilogue: digits -> float, undo the 2^rr row scales, add c and d terms -----------
   // cacc holds the lane's share of c * sum_k t_k for row my_beta of X; dacc the d term.
@@ -669,24 +679,32 @@ static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cu
       return BQQ_ERR_CUDA;
   }
   const bool merged = PT == 1 && NB == 1 && p.bpc > 1;   // such CTAs prepare x themselves
+  // Every kernel is launched as a programmatic dependent of whatever precedes it in the stream: it may
+  // become resident while that kernel still runs, prefetches weights, and executes griddepcontrol.wait
+  // before it reads activations or touches the workspace.  After a kernel that never triggers early
+  // (any kernel outside this library) this is an ordinary launch.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   if (!merged) {
     const int pairs = p.Mp * p.cwp;
-    bqq_xprep_kernel<QT><<<(pairs * 8 + 127) / 128, 128, 0, st>>>(
-        p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, NB, const_cast<uint8_t*>(p.xdig),
-        const_cast<float*>(p.xscale), const_cast<float*>(p.xsum), const_cast<float*>(p.xl1));
+    cudaLaunchConfig_t xc = {};
+    xc.gridDim = dim3((pairs * 8 + 127) / 128);
+    xc.blockDim = dim3(128);
+    xc.stream = st;
+    xc.attrs = attr;
+    xc.numAttrs = 1;
+    if (cudaLaunchKernelEx(&xc, bqq_xprep_kernel<QT>, p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, (int)NB,
+                           const_cast<uint8_t*>(p.xdig), const_cast<float*>(p.xscale), const_cast<float*>(p.xsum),
+                           const_cast<float*>(p.xl1)) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   }
-  // decode kernel: programmatic dependent launch after the preparation kernel, so that its weight
-  // copies overlap the preparation; the kernel itself waits before it touches the prepared x
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.rw * (p.bw / p.bpc) * p.nchunks, pl.mtiles);
   cfg.blockDim = dim3(kDT * p.bpc);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = merged ? 0 : 1;
+  cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
 }

@@ -49,6 +49,9 @@ __device__ __forceinline__ uint2 ld_slot(const uint2* p) {
 __global__ void __launch_bounds__(kPeerThreads)
 bqq_peer_gather_kernel(const PeerArgs a) {
   __shared__ int s_giveup;
+  // started as a programmatic dependent of the kernel that produces the slice: wait for the producer
+  // before reading anything
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned* mine = reinterpret_cast<unsigned*>(a.regions[a.rank]);
   const int tid = threadIdx.x;
   const long long gtid = (long long)blockIdx.x * kPeerThreads + tid, gthreads = (long long)gridDim.x * kPeerThreads;
@@ -86,6 +89,7 @@ bqq_peer_gather_kernel(const PeerArgs a) {
     a.out[r * a.ld_out + c] = v.x;
   }
   __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel of the stream may become resident
   if (s_giveup && tid == 0) atomicExch(mine + 1, 1u);
 
   // the last block to finish advances the sequence number (every block has read it by then)
@@ -172,7 +176,16 @@ int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int r
   const long long words = (long long)rows * a.row_words * g->world;
   int blocks = (int)((words + 2 * kPeerThreads - 1) / (2 * kPeerThreads));
   blocks = blocks < 1 ? 1 : (blocks > kPeerMaxBlocks ? kPeerMaxBlocks : blocks);
-  bqq_peer_gather_kernel<<<blocks, kPeerThreads, 0, (cudaStream_t)stream>>>(a);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(kPeerThreads);
+  cfg.stream = (cudaStream_t)stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, bqq_peer_gather_kernel, a) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
 }
 
