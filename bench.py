@@ -236,9 +236,10 @@ def main():
     def step():
         with torch.no_grad():
             for n, (L, x) in enumerate(zip(layers, xs)):
-                y = L(x)
                 if world > 1:
-                    peer.gather(y, out=gathers[n])     # peer-to-peer stores, one kernel per rank
+                    L.forward_gathered(x, peer, out=gathers[n])    # decode kernel stores its row patches to the peers
+                else:
+                    L(x)
 
     stream = torch.cuda.Stream(device)
     with torch.cuda.stream(stream):
@@ -280,9 +281,8 @@ def main():
             with torch.no_grad():
                 for n, L in enumerate(layers):
                     if world > 1:
-                        y = L(xh[n].to(device, non_blocking=True))
-                        peer.gather(y, out=gathers[n])
-                        yh[n].copy_(y, non_blocking=True)
+                        y = L.forward_gathered(xh[n].to(device, non_blocking=True), peer, out=gathers[n])
+                        yh[n].copy_(y[:, :yh[n].shape[1]], non_blocking=True)
                     else:
                         bound[n]()                        # one C call: copy in, kernels, copy out
             stream.synchronize()
@@ -321,7 +321,7 @@ def main():
             'config': {'workload': 'decode_sweep_b1', 'layers': len(cfgs), 'P': P, 'Q': Q, 'r': R,
                        'activations': 'bf16', 'batch': 1, 'bytes_per_step_per_gpu': step_bytes,
                        'l2': 'working set per step (208.5 MB of packed planes) exceeds the 126 MB L2',
-                       'parallelism': f'row-patch shards x{world}, outputs gathered by peer-to-peer stores (bqq_peer_gather)' if world > 1 else 'single GPU'},
+                       'parallelism': f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel (bqq_forward_decode_gathered)' if world > 1 else 'single GPU'},
             'e2e': {'value': e2e_val, 'unit': 'GB/s',
                     'h2d_bytes_per_step': sum(i * 2 for (o, i, bw) in cfgs),
                     'd2h_bytes_per_step': sum(o * 2 for (o, i, bw) in cfgs),

@@ -26,7 +26,7 @@ EXPORTS = [
     'bqq_decode_launches', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
     'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc',
     'bqq_peer_region_bytes', 'bqq_peer_alloc', 'bqq_peer_open', 'bqq_peer_close', 'bqq_peer_free',
-    'bqq_peer_gather', 'bqq_peer_status',
+    'bqq_peer_gather', 'bqq_peer_status', 'bqq_forward_decode_gathered',
 ]
 
 
@@ -85,6 +85,8 @@ def _load():
         'bqq_peer_free': (i32, [vp]),
         'bqq_peer_gather': (i32, [C.POINTER(BqqPeerGroup), vp, i32, i32, i64, i64, vp, i64, vp]),
         'bqq_peer_status': (i32, [C.POINTER(BqqPeerGroup), vp]),
+        'bqq_forward_decode_gathered': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, C.POINTER(BqqPeerGroup), vp, i64,
+                                            vp, sz, vp]),
         'bqq_noalloc_scratch_bytes': (sz, []),
         'bqq_forward_decode_noalloc': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp]),
     }

@@ -189,6 +189,51 @@ class _BqqForwardMixin:
                       'bqq_forward_prefill')
         return y.reshape(*X.shape[:-1], out_f)
 
+    def forward_gathered(self, X, peer, out=None):
+        """Forward of a row-patch shard with the column gather built in: every rank calls it on its
+        shard with the full activation X [..., in] and gets the full output [..., world*out_local]
+        (columns in rank order).  `peer` is a bqq_b200.peer.PeerGatherGroup of the ranks.
+
+        Up to 16 rows the decode kernel itself stores each finished row patch into the peers' gather
+        regions (bqq_forward_decode_gathered); larger batches run the forward and then the gather kernel."""
+        self._check_inference_only(X)
+        if X.dtype not in _DTYPE_CODE:
+            raise RuntimeError(f'bqq_b200: unsupported activation dtype {X.dtype} (fp32, bf16, fp16 only)')
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        in_f = self.col_width * self.z_col
+        out_f = self.row_width * self.y_row
+        if X.shape[-1] != in_f:
+            raise RuntimeError(f'bqq_b200: last dim of X is {X.shape[-1]}, layer expects {in_f}')
+        X = X.to(device)
+        x2 = X.reshape(-1, in_f)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        esize = X.element_size()
+        fused = (0 < M <= _cabi.DECODE_MAX_M and (out_f * esize) % 4 == 0
+                 and (esize == 4 or self.y_row % 2 == 0)
+                 and M * out_f * peer.world * esize <= peer.max_bytes)
+        if not fused:
+            return peer.gather(self.forward(X), out=out)
+        if out is None:
+            out = torch.empty((M, peer.world * out_f), dtype=X.dtype, device=device)
+        o2 = out.reshape(M, peer.world * out_f)
+        if o2.data_ptr() != out.data_ptr() or o2.stride(-1) != 1 or out.dtype != X.dtype:
+            raise RuntimeError('bqq_b200: `out` must be a [rows, world*out] tensor of the input dtype with unit inner stride')
+        y = torch.empty((M, out_f), dtype=X.dtype, device=device)
+        code = _DTYPE_CODE[X.dtype]
+        layer = self._layer(st)
+        with torch.cuda.device(device):
+            nbytes = lib.bqq_decode_workspace_bytes(st.dims, M)
+            ws = _workspace(device, 'decode', nbytes)
+            check(lib.bqq_forward_decode_gathered(layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(), code,
+                                                  y.stride(0), peer.descriptor(), o2.data_ptr(), o2.stride(0),
+                                                  ws.data_ptr(), ws.numel(),
+                                                  torch.cuda.current_stream(device).cuda_stream),
+                  'bqq_forward_decode_gathered')
+        return o2.reshape(*X.shape[:-1], peer.world * out_f)
+
     def bind_host(self, X_host, out=None):
         """Prepare the forward for activations that live in HOST memory and return `(run, out)`.
 

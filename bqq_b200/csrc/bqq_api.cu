@@ -25,6 +25,18 @@ static int check_io(const BqqLayer* L, const void* x, int x_dtype, int M, int64_
   return BQQ_OK;
 }
 
+// bqq_forward_decode, optionally with the peer stores of bqq_forward_decode_gathered (not exported in the header)
+int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer) {
+  int rc = check_layer(layer);
+  if (rc) return rc;
+  rc = check_io(layer, x, x_dtype, M, ldx, y, y_dtype, ldy);
+  if (rc) return rc;
+  if (M > BQQ_DECODE_MAX_M) return BQQ_ERR_UNSUPPORTED;
+  return decode_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
+                       (cudaStream_t)stream, peer);
+}
+
 extern "C" {
 
 int bqq_abi_version(void) { return BQQ_ABI_VERSION; }
@@ -65,13 +77,7 @@ size_t bqq_decode_workspace_bytes(const BqqDims* dims, int M) {
 
 int bqq_forward_decode(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                        int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
-  int rc = check_layer(layer);
-  if (rc) return rc;
-  rc = check_io(layer, x, x_dtype, M, ldx, y, y_dtype, ldy);
-  if (rc) return rc;
-  if (M > BQQ_DECODE_MAX_M) return BQQ_ERR_UNSUPPORTED;
-  return decode_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
-                       (cudaStream_t)stream);
+  return bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream, nullptr);
 }
 
 size_t bqq_prefill_workspace_bytes(const BqqDims* dims, int M) {

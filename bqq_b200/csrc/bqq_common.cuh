@@ -126,9 +126,14 @@ inline int launch_status() {
 }
 
 // Entry points implemented in the other translation units.
+// `peer` (may be NULL): the decode kernel also stores its outputs into the peers' gather regions
 int decode_launch(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
-                  int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream);
+                  int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream,
+                  const BqqPeerGroup* peer = nullptr);
+size_t peer_half_bytes(size_t gather_bytes);   // bytes of one half of a peer region's slot area
 size_t decode_workspace_bytes(const BqqDims* dims, int M);
+constexpr size_t kPeerCtrlBytes = 512;   // control words at the start of a peer gather region (bqq_peer.cu)
+
 int decode_launches(const BqqDims* dims, int M);   // kernels per decode call: 1 or 2
 size_t decode_counter_bytes();   // leading part of the decode workspace that must start zeroed
 int reconstruct_launch(const BqqLayer* layer, void* W, void* W_lo, int w_dtype, float scale,

@@ -63,7 +63,7 @@ size_t decode_workspace_bytes(const BqqDims* dims, int M) {
 }
 
 int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t ldx, void* y,
-                  int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t st) {
+                  int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t st, const BqqPeerGroup* peer) {
   Geom g(L->dims);
   DecodePlan pl = make_decode_plan(g, M);
   if (pl.variant < 0) return BQQ_ERR_UNSUPPORTED;
@@ -97,6 +97,18 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
   p.coef_vec = (L->coef_dtype == BQQ_F32 && g.cw % 4 == 0 && (((uintptr_t)L->a | (uintptr_t)L->b |
                                                                  (uintptr_t)L->c | (uintptr_t)L->d) & 15) == 0)
                    ? 1 : 0;
+  for (int q = 0; q < BQQ_MAX_PEERS; ++q) p.peer_regions[q] = nullptr;
+  p.peer_world = p.peer_rank = p.peer_row_words = 0;
+  p.peer_half = 0;
+  if (peer) {
+    const size_t es = dtype_size(y_dtype);
+    if (((size_t)g.out_features() * es) % 4 || (es == 2 && (g.P & 1))) return BQQ_ERR_MISALIGNED;   // outputs travel as 32-bit words
+    for (int q = 0; q < peer->world; ++q) p.peer_regions[q] = reinterpret_cast<uint8_t*>(peer->regions[q]);
+    p.peer_world = peer->world;
+    p.peer_rank = peer->rank;
+    p.peer_row_words = (int)((size_t)g.out_features() * es / 4);
+    p.peer_half = peer_half_bytes(peer->gather_bytes);
+  }
   switch (pl.variant) {
     case 0: return decode_launch_variant<0>(p, pl, st);
     case 1: return decode_launch_variant<1>(p, pl, st);

@@ -71,6 +71,11 @@ struct DecodeParams {
   int PTg, QTg, RTg;       // 32-blocks of the planes as packed
   int JG, NS;
   int sgw, nchunks, mtiles, bpc;
+  // optional peer-to-peer send of the outputs (row-patch shards; all zero when unused): the regions of
+  // every rank as mapped here, this rank, words of one local output row, bytes of one slot half
+  uint8_t* peer_regions[BQQ_MAX_PEERS];
+  int peer_world, peer_rank, peer_row_words;
+  unsigned long long peer_half;
   int coef_vec;            // 1: fp32 coefficients, cw % 4 == 0, 16-byte aligned -> 128-bit loads
 };
 
@@ -212,6 +217,33 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
   const int m = inside ? pair / cwp : 0, j = inside ? pair % cwp : 0;
   xprep_pair<QT>(x, x_dtype, ldx, Q, NB, cwp / kGroup, inside, inside && m < M && j < cw, m, j, m / NB, m % NB,
                  threadIdx.x & 7, reinterpret_cast<uint32_t*>(xdig), xscale, xsum, xl1, pair);
+}
+
+// Final output of one lane (row `row` of X, local output column `o`) also travels to every rank of a
+// peer gather group: the 32-bit word that holds it goes with the gather's sequence number as one
+// 8-byte store into slot [row][rank-major column] of every region (see bqq_peer.cu).  16-bit outputs
+// are paired with the neighbouring lane's (o is even on even lanes).  Every lane of the warp calls it.
+__device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int row, int o, float v, int lane) {
+  uint32_t word;
+  bool sender = valid;
+  if (p.y_dtype == BQQ_F32) {
+    word = __float_as_uint(v);
+  } else {
+    const uint32_t h = p.y_dtype == BQQ_BF16 ? (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                              : (uint32_t)__half_as_ushort(__float2half_rn(v));
+    const uint32_t up = __shfl_down_sync(0xffffffffu, h, 1);
+    word = h | (up << 16);
+    sender = valid && !(lane & 1);
+  }
+  if (!sender) return;
+  const unsigned* mine = reinterpret_cast<const unsigned*>(p.peer_regions[p.peer_rank]);
+  const unsigned count = *reinterpret_cast<const volatile unsigned*>(mine) + 1u;
+  const unsigned seq = count | 0x80000000u;
+  const size_t wcol = p.y_dtype == BQQ_F32 ? (size_t)o : (size_t)o >> 1;
+  const size_t slot = ((size_t)row * p.peer_world + p.peer_rank) * p.peer_row_words + wcol;
+  const size_t off = kPeerCtrlBytes + (count & 1u) * p.peer_half + slot * 8;
+  for (int q = 0; q < p.peer_world; ++q)
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.peer_regions[q] + off), "r"(word), "r"(seq) : "memory");
 }
 
 // MB: the CTA takes all bit layers of its row patch (4 warps each) instead of one.
@@ -631,11 +663,13 @@ bqq_decode_kernel(const DecodeParams p) {
       const int beta = idx / PP, pp = idx % PP;
       float v = 0.f;
       for (int w = 0; w < nwarps; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
-      if (pp < p.P && m0 + beta < p.M) {
-        const int o = i * p.P + pp;
+      const bool valid = pp < p.P && m0 + beta < p.M;
+      const int o = i * p.P + pp;
+      if (valid) {
         if (p.bias) v += load_as_float(p.bias, o, p.bias_dtype);
         store_from_float(p.y, (size_t)(m0 + beta) * p.ldy + o, p.y_dtype, v);
       }
+      if (p.peer_world) peer_send(p, valid, m0 + beta, o, v, lane);
     }
     return;
   }
@@ -658,14 +692,16 @@ bqq_decode_kernel(const DecodeParams p) {
   if (ticket != (unsigned)(nparts - 1)) return;
   for (int idx = lane; idx < NB * PP; idx += 32) {
     const int beta = idx / PP, pp = idx % PP;
-    if (pp < p.P && m0 + beta < p.M) {
-      float v = 0.f;
+    const bool valid = pp < p.P && m0 + beta < p.M;
+    const int o = i * p.P + pp;
+    float v = 0.f;
+    if (valid) {
       for (int sp = 0; sp < nparts; ++sp)
         v += __ldcg(p.partial + ((size_t)sp * mrows + m0 + beta) * out_stride + (size_t)i * PP + pp);
-      const int o = i * p.P + pp;
       if (p.bias) v += load_as_float(p.bias, o, p.bias_dtype);
       store_from_float(p.y, (size_t)(m0 + beta) * p.ldy + o, p.y_dtype, v);
     }
+    if (p.peer_world) peer_send(p, valid, m0 + beta, o, v, lane);
   }
   if (lane == 0) p.counters[i * p.mtiles + blockIdx.y] = 0u;   // ready for the next call
 }

@@ -20,16 +20,20 @@
 
 #include "bqq_common.cuh"
 
+// bqq_forward_decode with the peer group handed through to the kernel (bqq_api.cu)
+int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer);
+
 namespace bqq {
 
-constexpr size_t kPeerCtrlBytes = 512;         // sequence number, status, block counter
 constexpr long long kPeerWaitBudget = 2000000000LL;   // clock cycles (~1 s) before a poll gives up
 constexpr int kPeerThreads = 256;
 constexpr int kPeerMaxBlocks = 32;
 
 struct PeerArgs {
   uint8_t* regions[BQQ_MAX_PEERS];             // every rank's region as mapped in this process
-  const uint32_t* src;                         // local slice, rows of `row_words` words, pitch ld_src words
+  const uint32_t* src;                         // local slice, rows of `row_words` words, pitch ld_src words;
+                                               // NULL: the producing kernel sends the slice itself
   uint32_t* out;                               // gathered rows, pitch ld_out words
   int rank, world, rows;
   int row_words;                               // 32-bit words of one row of the local slice
@@ -50,8 +54,9 @@ __global__ void __launch_bounds__(kPeerThreads)
 bqq_peer_gather_kernel(const PeerArgs a) {
   __shared__ int s_giveup;
   // started as a programmatic dependent of the kernel that produces the slice: wait for the producer
-  // before reading anything
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // before reading the slice.  When the producer sends the slice itself (src == NULL) the polling below
+  // may run while the producer still works, and the wait moves to the end.
+  if (a.src) asm volatile("griddepcontrol.wait;" ::: "memory");
   unsigned* mine = reinterpret_cast<unsigned*>(a.regions[a.rank]);
   const int tid = threadIdx.x;
   const long long gtid = (long long)blockIdx.x * kPeerThreads + tid, gthreads = (long long)gridDim.x * kPeerThreads;
@@ -63,7 +68,7 @@ bqq_peer_gather_kernel(const PeerArgs a) {
   __syncthreads();
 
   // send: my words into everybody's slots (my own included)
-  const long long nsend = (long long)a.rows * a.row_words;
+  const long long nsend = a.src ? (long long)a.rows * a.row_words : 0;
   for (long long w = gtid; w < nsend; w += gthreads) {
     const long long r = w / a.row_words, c = w - r * a.row_words;
     const uint32_t data = a.src[r * a.ld_src + c];
@@ -89,6 +94,9 @@ bqq_peer_gather_kernel(const PeerArgs a) {
     a.out[r * a.ld_out + c] = v.x;
   }
   __syncthreads();
+  // every slot has arrived, so a sending producer has issued all its stores; it must also have ended
+  // before this grid ends, because later kernels only wait for this one
+  if (!a.src) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel of the stream may become resident
   if (s_giveup && tid == 0) atomicExch(mine + 1, 1u);
 
@@ -100,14 +108,15 @@ bqq_peer_gather_kernel(const PeerArgs a) {
   }
 }
 
+// a region = control words + two halves of 8-byte slots (one per 32-bit word of the largest gathered result)
+size_t peer_half_bytes(size_t gather_bytes) { return (2 * gather_bytes + 255) / 256 * 256; }
+
 }  // namespace bqq
 
 using namespace bqq;
 
 extern "C" {
 
-// control words + two halves of 8-byte slots (one per 32-bit word of the largest gathered result)
-static inline size_t peer_half_bytes(size_t gather_bytes) { return (2 * gather_bytes + 255) / 256 * 256; }
 size_t bqq_peer_region_bytes(size_t gather_bytes) { return kPeerCtrlBytes + 2 * peer_half_bytes(gather_bytes); }
 
 int bqq_peer_alloc(size_t gather_bytes, void** region, unsigned char handle[BQQ_PEER_HANDLE_BYTES]) {
@@ -149,9 +158,10 @@ int bqq_peer_free(void* region) {
   return BQQ_OK;
 }
 
-int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int rows, int64_t n_local, int64_t ldy,
-                    void* gathered, int64_t ld_gathered, void* stream) {
-  if (!g || !y_local) return BQQ_ERR_NULL;
+// y_local == NULL: receive only (the slices are sent by the kernels that produce them)
+static int peer_gather_launch(const BqqPeerGroup* g, const void* y_local, int dtype, int rows, int64_t n_local,
+                              int64_t ldy, void* gathered, int64_t ld_gathered, void* stream) {
+  if (!g) return BQQ_ERR_NULL;
   if (g->world < 1 || g->world > BQQ_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return BQQ_ERR_BAD_SHAPE;
   const size_t es = dtype_size(dtype);
   if (!es) return BQQ_ERR_DTYPE;
@@ -159,7 +169,7 @@ int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int r
   if (rows <= 0 || n_local <= 0 || ldy < n_local || ld_gathered < n_local * g->world) return BQQ_ERR_BAD_SHAPE;
   if ((size_t)rows * n_local * g->world * es > g->gather_bytes) return BQQ_ERR_WORKSPACE;
   if (((size_t)n_local * es) % 4 || ((size_t)ldy * es) % 4 || ((size_t)ld_gathered * es) % 4 ||
-      ((uintptr_t)y_local & 3) || ((uintptr_t)gathered & 3))
+      (y_local && ((uintptr_t)y_local & 3)) || ((uintptr_t)gathered & 3))
     return BQQ_ERR_MISALIGNED;                                  // slices travel as 32-bit words
   PeerArgs a;
   for (int q = 0; q < g->world; ++q) {
@@ -187,6 +197,31 @@ int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int r
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, bqq_peer_gather_kernel, a) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
+}
+
+int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int rows, int64_t n_local, int64_t ldy,
+                    void* gathered, int64_t ld_gathered, void* stream) {
+  if (!y_local) return BQQ_ERR_NULL;
+  return peer_gather_launch(g, y_local, dtype, rows, n_local, ldy, gathered, ld_gathered, stream);
+}
+
+int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y_local,
+                                int y_dtype, int64_t ldy, const BqqPeerGroup* g, void* gathered, int64_t ld_gathered,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (!layer || !g || !gathered) return BQQ_ERR_NULL;
+  if (g->world < 1 || g->world > BQQ_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return BQQ_ERR_BAD_SHAPE;
+  if (M <= 0 || M > BQQ_DECODE_MAX_M) return BQQ_ERR_BAD_SHAPE;
+  for (int q = 0; q < g->world; ++q)
+    if (!g->regions[q]) return BQQ_ERR_NULL;
+  Geom geo(layer->dims);
+  const size_t es = dtype_size(y_dtype);
+  if (!es) return BQQ_ERR_DTYPE;
+  if ((size_t)M * geo.out_features() * g->world * es > g->gather_bytes) return BQQ_ERR_WORKSPACE;
+  // same argument checks as bqq_forward_decode, then the decode kernel with the peer stores in its
+  // epilogue, then the receiving kernel (programmatic dependent: it polls while the decode kernel ends)
+  int rc = bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y_local, y_dtype, ldy, workspace, workspace_bytes, stream, g);
+  if (rc) return rc;
+  return peer_gather_launch(g, nullptr, y_dtype, M, geo.out_features(), geo.out_features(), gathered, ld_gathered, stream);
 }
 
 int bqq_peer_status(const BqqPeerGroup* g, void* stream) {

@@ -54,6 +54,10 @@ class PeerGatherGroup:
         self._desc = BqqPeerGroup(self.rank, self.world, (C.c_void_p * _cabi.MAX_PEERS)(*self._regions),
                                   self.max_bytes)
 
+    def descriptor(self):
+        """ctypes reference to the BqqPeerGroup of this rank (for the C entry points)."""
+        return C.byref(self._desc)
+
     def gather(self, y_local: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """y_local [..., n] on every rank -> [..., world*n] (columns in rank order) on every rank."""
         lead, n = y_local.shape[:-1], y_local.shape[-1]

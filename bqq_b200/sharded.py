@@ -55,7 +55,9 @@ class ColumnParallelBinaryQuadratic(nn.Module):
         self.shard = shard_rows(full, rank, world)
 
     def forward(self, X):
+        if self.gather and self.world > 1 and self.peer is not None:
+            return self.shard.forward_gathered(X, self.peer)      # decode kernel sends its row patches itself
         y = self.shard(X)
         if not self.gather or self.world == 1:
             return y
-        return gather_columns(y, self.group, peer=self.peer)
+        return gather_columns(y, self.group)

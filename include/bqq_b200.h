@@ -258,6 +258,22 @@ int bqq_peer_gather(const BqqPeerGroup* group, const void* y_local, int dtype, i
 int bqq_peer_status(const BqqPeerGroup* group, void* stream);
 
 /*
+ * bqq_forward_decode of a row-patch shard fused with the gather: the decode
+ * kernel's epilogue stores every finished output row patch into the gather
+ * regions of all ranks while the rest of the kernel still runs, and a second
+ * kernel (started while the first one ends) waits for the peers' row patches and
+ * writes the full rows [M, world*out_local] to `gathered`.  y_local [M, out_local]
+ * still receives this rank's columns.  Same rules as bqq_forward_decode and
+ * bqq_peer_gather; 16-bit outputs need an even P.  This is the sharded forward a
+ * column-parallel wrapper of the reference module would need (the reference has no
+ * multi-GPU path).
+ */
+int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
+                                void* y_local, int y_dtype, int64_t ldy,
+                                const BqqPeerGroup* group, void* gathered, int64_t ld_gathered,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Dense weight W [rw*P, cw*Q] row-major in element type w_dtype: the value of
  * BinaryQuadratic.get_weight (src/bqq_modules.py:48-55), built with AND +
  * popcount like reconstruct_W_kernel (src/bqq_cuda.cu:198-246) but with

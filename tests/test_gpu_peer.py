@@ -70,6 +70,22 @@ def _worker(rank, world, port, result_dir):
                 assert torch.equal(out.cpu(), want), (rank, 'replay', rep)
             graph.reset()
             grp.status()
+        # the forward with the gather built in: every rank's shard sends its row patches from the decode
+        # kernel's epilogue; the result equals the unsharded layer bit for bit
+        from bqq_b200.bqq_modules import BinaryQuadratic, shard_rows
+        from tests.helpers import synth_layer
+        for (bw, rw, cw, M, dtype, bias) in [(2, 8, 6, 1, torch.bfloat16, True), (3, 4, 136, 1, torch.float32, False),
+                                             (2, 8, 6, 5, torch.float16, True), (2, 6, 40, 16, torch.bfloat16, False)]:
+            Y, Z, A, b, X = synth_layer(bw, rw, cw, 32, 32, 32, M, seed=31, bias=bias)
+            full = BinaryQuadratic(Y.float(), Z.float(), A, bias=b if bias else None).to(dev)
+            Xd = X.to(dtype).to(dev)
+            with torch.no_grad():
+                want = full(Xd)
+                shard = shard_rows(full, rank, world)
+                for _ in range(2):
+                    got = shard.forward_gathered(Xd, grp)
+                    assert torch.equal(got, want), (rank, bw, rw, cw, M)
+        grp.status()
         grp.close()
         with open(os.path.join(result_dir, f'ok{rank}'), 'w') as f:
             f.write('ok')
