@@ -35,6 +35,7 @@ def main():
     ap.add_argument('--prompt', type=int, default=512)
     ap.add_argument('--new', type=int, default=128)
     ap.add_argument('--repeats', type=int, default=3)
+    ap.add_argument('--nccl-gathers', action='store_true', help='gather with the process group instead of peer stores')
     args = ap.parse_args()
 
     rank = int(os.environ.get('RANK', '0'))
@@ -48,7 +49,12 @@ def main():
     cfg = StackConfig(layers=args.layers, hidden=args.hidden, intermediate=args.intermediate, heads=args.heads,
                       kv_heads=args.kv_heads, vocab=args.vocab, bit_width=args.bits, group=args.group,
                       max_seq=args.prompt + args.new)
-    model = DecoderStack(cfg, device, seed=0, rank=rank, world=world)
+    peer = None
+    if world > 1 and not args.nccl_gathers:
+        from .peer import PeerGatherGroup
+        # decode-sized gathers (one row per sequence) go peer to peer; the prefill's stay on the process group
+        peer = PeerGatherGroup(args.batch * max(cfg.intermediate, cfg.hidden, cfg.vocab) * 2, device)
+    model = DecoderStack(cfg, device, seed=0, rank=rank, world=world, peer=peer)
     gen = torch.Generator(device=device).manual_seed(1)
     prompt = torch.randint(0, cfg.vocab, (args.batch, args.prompt), generator=gen, device=device)
     cache = model.new_cache(args.batch)
@@ -97,6 +103,7 @@ def main():
             'decode_ms_per_step': best_decode / steps,
             'prefill_ms': best_prefill, 'prefill_tokens_per_s': args.batch * args.prompt / (best_prefill * 1e-3),
             'bqq_bytes_per_token_per_gpu': model.bqq_bytes_per_token(),
+            'gathers': 'none' if world == 1 else ('nccl' if peer is None else 'peer stores'),
             'lm_head': 'dense bf16, included', 'data': 'synthetic (random init, random prompt ids)'}),
             flush=True)
     graph.reset()
@@ -106,6 +113,9 @@ def main():
         timer = threading.Timer(30.0, lambda: os._exit(0))     # teardown must never hang the job
         timer.daemon = True
         timer.start()
+        if peer is not None:
+            peer.status()
+            peer.close()
         dist.barrier()
         dist.destroy_process_group()
         timer.cancel()

@@ -13,7 +13,10 @@ Only the BinaryQuadratic layers are the product here; normalisation, rotary embe
 attention and the dense lm_head are plain torch ops (plumbing).  With world > 1 the layers are
 column-parallel (bqq_b200/sharded.py): q/k/v are sharded by heads so attention runs on local
 heads, gate/up share one sharding so SwiGLU is local, o_proj and down_proj are row-patch
-sharded; four all-gathers per layer, all without reductions.
+sharded; four gathers per layer, all without reductions.  With a PeerGatherGroup the gathers are the
+library's peer-to-peer stores (o_proj and down_proj send their row patches from the decode kernel's
+epilogue, the attention output and the SwiGLU product go through the gather kernel); results too large
+for the group's buffers (prefill) fall back to the process group's all-gather.
 """
 from __future__ import annotations
 
@@ -63,9 +66,9 @@ def random_bq(out_f: int, in_f: int, cfg: StackConfig, device, gen) -> BinaryQua
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: StackConfig, device, gen, rank: int, world: int):
+    def __init__(self, cfg: StackConfig, device, gen, rank: int, world: int, peer=None):
         super().__init__()
-        self.cfg, self.rank, self.world = cfg, rank, world
+        self.cfg, self.rank, self.world, self.peer = cfg, rank, world, peer
         hd = cfg.head_dim
         self.local_heads = cfg.heads // world
         self.local_kv = max(1, cfg.kv_heads // world)
@@ -83,8 +86,24 @@ class DecoderLayer(nn.Module):
         self.norm1 = nn.Parameter(torch.ones(h, device=device, dtype=torch.bfloat16))
         self.norm2 = nn.Parameter(torch.ones(h, device=device, dtype=torch.bfloat16))
 
+    def _fits(self, rows, cols, esize):
+        return self.peer is not None and rows * cols * self.world * esize <= self.peer.max_bytes
+
     def _gather(self, y):
-        return gather_columns(y) if self.world > 1 else y
+        if self.world == 1:
+            return y
+        if self._fits(y.numel() // y.shape[-1], y.shape[-1], y.element_size()):
+            return self.peer.gather(y)
+        return gather_columns(y)
+
+    def _proj_gathered(self, proj, x):
+        """Row-patch sharded projection with its outputs gathered on every rank."""
+        if self.world == 1:
+            return proj(x)
+        rows = x.numel() // x.shape[-1]
+        if rows <= 16 and self._fits(rows, proj.row_width * proj.y_row, x.element_size()):
+            return proj.forward_gathered(x, self.peer)
+        return self._gather(proj(x))
 
     def forward(self, x, k_cache, v_cache, pos, cos, sin, mask=None):
         """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim].
@@ -110,11 +129,11 @@ class DecoderLayer(nn.Module):
             v_cache.index_copy_(2, pos, v)
             att = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=mask, enable_gqa=True)
         att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
-        x = x + self._gather(self.o_proj(att))                                              # gather 2
+        x = x + self._proj_gathered(self.o_proj, att)                                       # gather 2
         hx = F.rms_norm(x, (cfg.hidden,), self.norm2, 1e-5)
         act = F.silu(self.gate_proj(hx)) * self.up_proj(hx)
         act = self._gather(act)                                                             # gather 3
-        return x + self._gather(self.down_proj(act))                                        # gather 4
+        return x + self._proj_gathered(self.down_proj, act)                                 # gather 4
 
 
 def _rope(x, cos, sin):
@@ -124,13 +143,13 @@ def _rope(x, cos, sin):
 
 
 class DecoderStack(nn.Module):
-    def __init__(self, cfg: StackConfig, device, seed: int = 0, rank: int = 0, world: int = 1):
+    def __init__(self, cfg: StackConfig, device, seed: int = 0, rank: int = 0, world: int = 1, peer=None):
         super().__init__()
-        self.cfg, self.rank, self.world, self.device = cfg, rank, world, device
+        self.cfg, self.rank, self.world, self.device, self.peer = cfg, rank, world, device, peer
         gen = torch.Generator(device=device).manual_seed(seed + 7919 * rank)
         shared = torch.Generator(device=device).manual_seed(seed)            # identical on every rank
         self.embed = (torch.randn(cfg.vocab, cfg.hidden, generator=shared, device=device) * 0.5).to(torch.bfloat16)
-        self.layers = nn.ModuleList(DecoderLayer(cfg, device, gen, rank, world) for _ in range(cfg.layers))
+        self.layers = nn.ModuleList(DecoderLayer(cfg, device, gen, rank, world, peer) for _ in range(cfg.layers))
         self.norm = torch.ones(cfg.hidden, device=device, dtype=torch.bfloat16)
         # dense bf16 lm_head, vocabulary sharded over the ranks
         self.lm_head = (torch.randn(cfg.vocab // world, cfg.hidden, generator=gen, device=device)
@@ -159,7 +178,11 @@ class DecoderStack(nn.Module):
         h = F.rms_norm(x_last, (self.cfg.hidden,), self.norm, 1e-5)
         logits = h @ self.lm_head.T                               # [B, vocab/world]
         if self.world > 1:
-            logits = gather_columns(logits)
+            rows = logits.numel() // logits.shape[-1]
+            if self.peer is not None and rows * logits.shape[-1] * self.world * logits.element_size() <= self.peer.max_bytes:
+                logits = self.peer.gather(logits)
+            else:
+                logits = gather_columns(logits)
         return logits.argmax(dim=-1)
 
     @torch.no_grad()
