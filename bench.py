@@ -38,7 +38,7 @@ SHAPES = [(2048, 2048), (2048, 6144), (6144, 2048), (4096, 14336)]   # (out, in)
 BITS = [2, 3, 4]
 P = Q = R = 32
 L2_BYTES = 126e6
-TRAFFIC_RATIO = 62.15 / 61.72   # measured DRAM bytes / algorithmic bytes (profiles/decode_kernel_4096x14336_bw4_m1.md)
+62.09 / 61.72   # measured DRAM bytes / algorithmic bytes (profiles/decode_kernel_4096x14336_bw4_m1.md)
 
 
 def sweep():
@@ -331,7 +331,7 @@ def main():
             'roofline': {'bound': 'hbm', 'achieved': per_gpu, 'peak': peak, 'unit': 'GB/s',
                          'frac': per_gpu / peak, 'traffic': TRAFFIC_RATIO * step_bytes / len(cfgs),
                          'traffic_note': 'dram read+write bytes of one ncu capture (4096x14336, 4 bit layers: '
-                                         '62.15 MB for 61.72 MB algorithmic) scaled by algorithmic bytes',
+                                         '62.09 MB for 61.72 MB algorithmic) scaled by algorithmic bytes',
                          'peak_kind': peak_kind,
                          'kernel': 'bqq_decode_kernel',
                          'avg_launch_us': ms * 1e3 / (args.steps * len(cfgs)),

@@ -143,7 +143,9 @@ int bqq_repack_u8_planes(const uint8_t* Y_packed, const uint8_t* Z_packed, const
  *   bqq_forward_kernel (src/bqq_cuda.cu:47-180).  The first 256 KiB of the
  *   workspace (bqq_decode_workspace_bytes, 256-byte aligned) are counters that
  *   must be zero-filled once after allocation; the kernel leaves them zeroed,
- *   so one workspace serves layers of any shape.  Calls sharing a workspace
+ *   so one workspace serves layers of any shape (the last counter word turns
+ *   non-zero if a bounded device-side wait ever gave up).  A workspace is always
+ *   required.  Calls sharing a workspace
  *   must not overlap on the GPU.  Results do not depend on the number of row
  *   patches: a row shard reproduces its slice of the full output bit for bit.
  * bqq_forward_prefill: any M; rebuilds W once into the workspace and runs a
