@@ -38,7 +38,7 @@ SHAPES = [(2048, 2048), (2048, 6144), (6144, 2048), (4096, 14336)]   # (out, in)
 BITS = [2, 3, 4]
 P = Q = R = 32
 L2_BYTES = 126e6
-62.09 / 61.72   # measured DRAM bytes / algorithmic bytes (profiles/decode_kernel_4096x14336_bw4_m1.md)
+TRAFFIC_RATIO = 62.09 / 61.72   # measured DRAM bytes / algorithmic bytes (profiles/decode_kernel_4096x14336_bw4_m1.md)
 
 
 def sweep():
