@@ -33,6 +33,12 @@
 
 namespace bqq {
 
+#ifndef BQQ_MID_STAGES
+#define BQQ_MID_STAGES 3
+#endif
+#ifndef BQQ_NB4_REGS
+#define BQQ_NB4_REGS 80
+#endif
 constexpr int kDW = 4;                   // warps per CTA
 constexpr int kDT = kDW * 32;
 constexpr int kMaxCounters = 65536;      // fixed-size counter region at the start of the workspace
@@ -123,11 +129,11 @@ struct DecodeSmem {
     yoff = RT * QT * 512;                             // slot: uint4 Z[RT][QT][32] | Y[PT][RT][32] | X[NB][digit][QT][8]
     xoff = yoff + PT * RT * 512;
     slot = xoff + NB * 2 * QT * 128;
-    stages = slot <= 2048 ? 4 : (slot <= 4096 ? 3 : 2);
+    stages = slot <= 1280 ? 4 : (slot <= 4096 ? BQQ_MID_STAGES : 2);
     ring = o;  o += nwarps * stages * slot;
     coef = o;  o += bpc * 4 * nsg * 16;               // float [bit][a|b|c|d][nsg*4]
     meta = o;  o += bpc * NB * 3 * nsg * 16;          // float [bit][NB][scale|sum|l1][nsg*4]
-    udig = o;  o += nwarps * kGroup * NB * 4 * RT * 32;  // u8 [warps][4 sub][NB][4 slots][RP]
+    udig = o;  o += nwarps * kGroup * NB * (4 * RT * 32 + (NB == 1 ? 0 : 16));  // u8 [warps][4 sub][NB][4 slots][RP] (+ pad)
     red = o;   o += nwarps * NB * PT * 32 * 4;        // f32 [warps][NB][PP]
     // CTAs that take all bit layers prepare x themselves: digits and statistics of the whole chunk
     xres = o;  o += bpc > 1 ? nsg * NB * 2 * QT * 128 : 0;   // uint4 [nsg][NB][digit][QT][8]
@@ -248,7 +254,7 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
 
 // MB: the CTA takes all bit layers of its row patch (4 warps each) instead of one.
 template <int PT, int QT, int RT, int NB, bool MB>
-__global__ void __maxnreg__(PT == 1 && NB == 1 ? 80 : 255)
+__global__ void __maxnreg__(PT == 1 ? (NB == 1 ? 80 : BQQ_NB4_REGS) : 255)
 bqq_decode_kernel(const DecodeParams p) {
   const int bpc = MB ? p.bpc : 1;
   constexpr int RP = RT * 32;
@@ -375,10 +381,14 @@ bqq_decode_kernel(const DecodeParams p) {
 
   // ---- digit exchange buffer: slots 0..2 are rewritten for every col patch, slot 3 is a column of
   // ones whose products count the Y bits of each row (removes the offset of the unsigned digits)
-  constexpr int kUSub = NB * 4 * RP;                 // bytes of one col patch's u digits
+  // [sub][row of X][slot][rank]; rows of X are 16 bytes further apart than their 4 slots need, so that the
+  // byte stores of lanes with different t (different rows of X) and the word loads of the two rows an
+  // n-tile covers fall into different banks
+  constexpr int kURow = 4 * RP + (NB == 1 ? 0 : 16);
+  constexpr int kUSub = NB * kURow;                  // bytes of one col patch's u digits
   uint8_t* my_udig = sm + L.udig + (size_t)warp * kGroup * kUSub;
   for (int e = lane; e < kGroup * kUSub / 4; e += 32)
-    reinterpret_cast<uint32_t*>(my_udig)[e] = (((4 * e) / RP) & 3) == 3 ? 0x01010101u : 0u;
+    reinterpret_cast<uint32_t*>(my_udig)[e] = (((4 * e) % kUSub) % kURow) / RP == 3 ? 0x01010101u : 0u;
   bool ok = mbar_wait(bar, 0);
 
   // ---- fold the x statistics into the coefficients of this warp's patch-bits (in place of the
@@ -464,13 +474,13 @@ bqq_decode_kernel(const DecodeParams p) {
   // the lane's row of X keeps scale and sum, where its u digits go and come from
   const int xlane = kXoff + (NB == 1 ? (g & 1) : g) * (QT * 8) + t;
   const float* mrow = smeta + my_beta * 3 * nsg * 4;   // [alpha | beta | gamma] of this lane's row of X
-  uint8_t* ust = my_udig + (NB == 1 ? g + 8 * t : t * 4 * RP + g);
+  uint8_t* ust = my_udig + (NB == 1 ? g + 8 * t : t * kURow + g);
   const uint8_t* uld[NT2];
 #pragma unroll
   for (int nt = 0; nt < NT2; ++nt) {
     const int beta = NB == 1 ? 0 : 2 * nt + (g >> 2);
     const int slot = NB == 1 ? min(g, 3) : (g & 3);      // slot 3: the column of ones
-    uld[nt] = my_udig + (beta * 4 + slot) * RP + 4 * t;
+    uld[nt] = my_udig + beta * kURow + slot * RP + 4 * t;
   }
 #pragma unroll(NB == 1 ? 4 : 1)
   for (int n = 0; n < nw; ++n) {

@@ -98,7 +98,8 @@ bqq_reconstruct_kernel(const ReconParams p) {
         int core = 0;
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) core += __popc(__shfl_sync(0xffffffffu, yr[rt], pp) & zc[rt]);
-        acc[pp] = fmaf(ca, (float)core, acc[pp]);
+        // int -> float on the FP32 pipe (core <= 64): 2^23 + core as a bit pattern, minus 2^23
+        acc[pp] = fmaf(ca, __int_as_float(0x4B000000 | core) - 8388608.f, acc[pp]);
       }
     }
     const int prow_max = min(32, g.P - 32 * pt);
