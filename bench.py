@@ -11,7 +11,8 @@ value  = algorithmic bytes (packed bits + fp32 coefficients + x + y) per second,
          all ranks, inputs resident in HBM, timed with CUDA events on the launching stream.
 e2e    = the same through module.bind_host (the C entry point bqq_forward_host) with HOST
          activations: pinned x -> device copy, forward, device -> pinned host copy of y, every
-         layer, every step, one stream synchronisation per step.
+         layer, every step (the step is captured once and replayed), one stream synchronisation
+         per step to read the outputs.
 With N > 1 ranks (weak scaling) each rank owns one row-patch shard of layers N times as
 tall (its shard has the base shape) and every layer's outputs are gathered on all ranks by the
 library's peer-to-peer store kernel (bqq_peer_gather; NCCL only carries the set-up and the timing
@@ -277,7 +278,7 @@ def main():
         with torch.no_grad():
             bound = [L.bind_host(xh[n], yh[n])[0] for n, L in enumerate(layers)] if world == 1 else None
 
-        def e2e_step():
+        def e2e_body():
             with torch.no_grad():
                 for n, L in enumerate(layers):
                     if world > 1:
@@ -285,6 +286,18 @@ def main():
                         yh[n].copy_(y[:, :yh[n].shape[1]], non_blocking=True)
                     else:
                         bound[n]()                        # one C call: copy in, kernels, copy out
+
+        for _ in range(3):
+            e2e_body()
+        stream.synchronize()
+        # a serving loop replays the whole step (copies in, kernels, copies out) as one captured graph and
+        # synchronises once per step to read the outputs
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph, stream=stream):
+            e2e_body()
+
+        def e2e_step():
+            e2e_graph.replay()
             stream.synchronize()
 
         for _ in range(3):
@@ -306,7 +319,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
 
-    shutdown(world, [graph], peer)          # communicator torn down before rank 0 spends time on the CPU baseline
+    shutdown(world, [graph, e2e_graph], peer)          # communicator torn down before rank 0 spends time on the CPU baseline
     if rank == 0:
         peak, peak_kind = peaks()
         total_bytes = step_bytes * world

@@ -112,6 +112,37 @@ int bqq_decode_launches(const BqqDims* dims, int M) {
   return decode_launches(dims, M);
 }
 
+// Device-visible address of pinned, mapped host memory (cudaHostAlloc / cudaHostRegister), or NULL.
+static void* mapped_device_pointer(const void* host) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, host) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (at.type != cudaMemoryTypeHost || !at.devicePointer) return nullptr;
+  return at.devicePointer;
+}
+
+// Rows of x from mapped host memory into the device staging buffer: 16 bytes per thread where the
+// alignment allows, 2 bytes otherwise.  Waits for the preceding kernel of the stream before writing.
+__global__ void __launch_bounds__(256)
+stage_host_rows_kernel(const uint8_t* __restrict__ src, long long ld_src, uint8_t* __restrict__ dst, long long row_bytes,
+                       int rows, int vec) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const long long tid = (long long)blockIdx.x * 256 + threadIdx.x, n = (long long)gridDim.x * 256;
+  if (vec) {
+    const long long per_row = row_bytes >> 4;
+    for (long long e = tid; e < per_row * rows; e += n) {
+      const long long r = e / per_row, c = e - r * per_row;
+      reinterpret_cast<uint4*>(dst + r * row_bytes)[c] = reinterpret_cast<const uint4*>(src + r * ld_src)[c];
+    }
+  } else {
+    const long long per_row = row_bytes >> 1;
+    for (long long e = tid; e < per_row * rows; e += n) {
+      const long long r = e / per_row, c = e - r * per_row;
+      reinterpret_cast<uint16_t*>(dst + r * row_bytes)[c] = reinterpret_cast<const uint16_t*>(src + r * ld_src)[c];
+    }
+  }
+}
+
 static inline size_t host_stage_bytes(size_t rows, size_t cols, int dtype) {
   return (rows * cols * dtype_size(dtype) + 255) / 256 * 256;
 }
@@ -139,6 +170,36 @@ int bqq_forward_host(const BqqLayer* layer, const void* x_host, int x_dtype, int
   char* xd = reinterpret_cast<char*>(workspace) + inner;
   char* yd = xd + host_stage_bytes(M, g.in_features(), x_dtype);
   cudaStream_t st = (cudaStream_t)stream;
+  // Small batches with pinned, mapped host buffers skip the copy engines (two DMA copies cost more than the
+  // decode kernel itself): the kernels read x from and write y to host memory directly.  Layers whose CTAs
+  // each read all of x first get it staged on the device by a small kernel.
+  if (M <= BQQ_DECODE_MAX_M) {
+    void* xm = mapped_device_pointer(x_host);
+    void* ym = mapped_device_pointer(y_host);
+    if (xm && ym) {
+      const void* xin = xm;
+      int64_t ld_in = ldx;
+      if (decode_launches(&layer->dims, M) == 1) {
+        const long long row_bytes = (long long)g.in_features() * xs;
+        const int vec = ((row_bytes | (long long)(ldx * xs) | (long long)(uintptr_t)xm | (long long)(uintptr_t)xd) & 15) == 0;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg = {};
+        const long long units = (row_bytes >> (vec ? 4 : 1)) * M;
+        cfg.gridDim = dim3((unsigned)((units + 255) / 256 > 64 ? 64 : (units + 255) / 256));
+        cfg.blockDim = dim3(256);
+        cfg.stream = st;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, stage_host_rows_kernel, (const uint8_t*)xm, (long long)(ldx * xs), (uint8_t*)xd, row_bytes,
+                               M, vec) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
+        xin = xd;
+        ld_in = g.in_features();
+      }
+      return bqq_forward(layer, xin, x_dtype, M, ld_in, ym, y_dtype, ldy, workspace, inner, stream);
+    }
+  }
   // the forward's own workspace comes first so that its zero-initialised counters stay where they were
   const size_t xrow = g.in_features() * xs, yrow = g.out_features() * ys;
   cudaError_t ce = (M == 1 || ldx == g.in_features())

@@ -186,7 +186,10 @@ int bqq_decode_launches(const BqqDims* dims, int M);
  * pageable memory the copies block the host).  It is what the reference module
  * does when it is handed a CPU tensor (`X.to(self.Y.device)`,
  * src/bqq_modules.py:35) without the per-call tensor allocations.  The caller
- * synchronises the stream before reading y_host.  The workspace must hold
+ * synchronises the stream before reading y_host.  For M <= 16 with pinned and
+ * mapped host buffers (cudaHostAlloc, cudaHostRegister, torch pin_memory) the
+ * kernels read x from and write y to host memory directly and no copy engine is
+ * involved; otherwise the two copies are cudaMemcpyAsync.  The workspace must hold
  * bqq_forward_host_workspace_bytes (the forward's workspace first, then the two
  * staging buffers), be 256-byte aligned and obey the decode workspace's
  * zero-initialisation rule.

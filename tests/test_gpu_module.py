@@ -165,3 +165,16 @@ def test_bind_host_reads_current_contents():
             assert run() is out
             torch.cuda.current_stream().synchronize()
             assert torch.equal(out.cuda(), _fwd(bq, xh.cuda()))
+
+
+def test_forward_host_with_pageable_buffers():
+    """Host buffers that are not pinned take the copy-engine route and give the same values."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(2, 4, 40, 32, 32, 32, 2, seed=23, bias=False)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    xh = X.to(torch.bfloat16)
+    out = torch.empty(2, 4 * 32, dtype=torch.bfloat16)
+    with torch.no_grad():
+        bq.forward_host(xh, out)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(out.cuda(), _fwd(bq, xh.cuda()))
