@@ -18,7 +18,7 @@ DECODE_MAX_M = 16
 EXPORTS = [
     'bqq_abi_version', 'bqq_strerror', 'bqq_device_supported',
     'bqq_zplane_words', 'bqq_yplane_words', 'bqq_algorithmic_bytes',
-    'bqq_pack_planes', 'bqq_unpack_planes', 'bqq_pack_planes_host', 'bqq_unpack_planes_host',
+    'bqq_pack_planes', 'bqq_unpack_planes', 'bqq_pack_planes_host', 'bqq_unpack_planes_host', 'bqq_pack_patch_host',
     'bqq_repack_u8_planes',
     'bqq_decode_workspace_bytes', 'bqq_forward_decode',
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
@@ -67,6 +67,7 @@ def _load():
         'bqq_unpack_planes': (i32, [vp, vp, dp, vp, vp, vp]),
         'bqq_pack_planes_host': (i32, [vp, vp, dp, vp, vp, vp, vp]),
         'bqq_unpack_planes_host': (i32, [vp, vp, dp, vp, vp]),
+        'bqq_pack_patch_host': (i32, [vp, vp, dp, i32, i32, i32, vp, vp]),
         'bqq_repack_u8_planes': (i32, [vp, vp, dp, vp, vp, vp, vp, vp]),
         'bqq_decode_workspace_bytes': (sz, [dp, i32]),
         'bqq_prefill_workspace_bytes': (sz, [dp, i32]),

@@ -439,6 +439,102 @@ class PackedBinaryQuadratic(_BqqForwardMixin, nn.Module):
         return self._weight_gpu(dtype)
 
 
+# ---------------------------------------------------------------------------
+# PlaneBinaryQuadratic: patch files straight into this library's bit planes
+# ---------------------------------------------------------------------------
+
+class PlaneBinaryQuadratic(_BqqForwardMixin, nn.Module):
+    """BQQ layer that holds only this library's 32-bit bit planes (buffers `zplanes`, `yplanes`,
+    int32) and the coefficients: what BinaryQuadratic derives at first use is here the stored form.
+    The reference has no such class; `from_patches` replaces get_matrices + BinaryQuadratic
+    (src/bqq_modules.py:485-507, 21-32) for loaders that want to skip the dense bool Y / Z
+    (32 times the planes' size as bytes on the host)."""
+
+    def __init__(self, zplanes, yplanes, a, b, c, d, dims, bias=None):
+        super().__init__()
+        (self.bit_width, self.row_width, self.col_width, self.y_row, self.z_col,
+         self.inter_dimension) = (int(v) for v in dims)
+        self.register_buffer('zplanes', zplanes)
+        self.register_buffer('yplanes', yplanes)
+        self.a, self.b = nn.Parameter(a), nn.Parameter(b)
+        self.c, self.d = nn.Parameter(c), nn.Parameter(d)
+        self.bias = nn.Parameter(bias) if bias is not None else None
+
+    @classmethod
+    def from_patches(cls, patch_list, bit_width, bias=None) -> 'PlaneBinaryQuadratic':
+        """Patch dicts {patch_row, patch_col, coeff, mat1, mat2, bit_idx} -> layer, one patch at a
+        time on the host (bqq_pack_patch_host).  Same rules as get_matrices: entries with
+        bit_idx >= bit_width are skipped, the geometry comes from the first entry, a later entry for
+        the same (bit, row, col) replaces the earlier one, missing patches are zero."""
+        rw = max(int(p['patch_row']) for p in patch_list) + 1
+        cw = max(int(p['patch_col']) for p in patch_list) + 1
+        first = patch_list[0]
+        P, r = first['mat1'].shape
+        Q = first['mat2'].shape[1]
+        dims = _cabi.dims(bit_width, rw, cw, P, Q, r)
+        nz, ny = lib.bqq_zplane_words(dims), lib.bqq_yplane_words(dims)
+        if nz == 0 or ny == 0:
+            raise RuntimeError(f'bqq_b200: unsupported patch geometry (P={P}, Q={Q}, r={r})')
+        zp = torch.zeros(nz, dtype=torch.int32)
+        yp = torch.zeros(ny, dtype=torch.int32)
+        A = torch.zeros((bit_width, rw, cw, 4), dtype=first['coeff'].dtype)
+        for p in patch_list:
+            k = int(p['bit_idx'])
+            if k >= bit_width:
+                continue
+            i, j = int(p['patch_row']), int(p['patch_col'])
+            A[k, i, j] = p['coeff']
+            m1 = (p['mat1'] > 0.5).to(torch.uint8).contiguous()
+            m2 = (p['mat2'] > 0.5).to(torch.uint8).contiguous()
+            if tuple(m1.shape) != (P, r) or tuple(m2.shape) != (r, Q):
+                raise RuntimeError('bqq_b200: patches of one layer must share one geometry')
+            check(lib.bqq_pack_patch_host(m1.data_ptr(), m2.data_ptr(), dims, k, i, j, zp.data_ptr(), yp.data_ptr()),
+                  'bqq_pack_patch_host')
+        coef = [A[..., n].unsqueeze(-1).unsqueeze(-1) for n in range(4)]
+        return cls(zp, yp, coef[0].clone(), coef[1].clone(), coef[2].clone(), coef[3].sum(dim=0),
+                   (bit_width, rw, cw, P, Q, r), bias=bias)
+
+    def _plane_sources(self):
+        return self.yplanes, self.zplanes
+
+    def _ensure_packed(self) -> _PackedState:
+        """The buffers are the packed state: nothing is derived or copied."""
+        st = self._state()
+        _require_cuda(self.zplanes, 'the bit plane buffer')
+        pkey = (_tensor_key(self.yplanes), _tensor_key(self.zplanes))
+        if st.plane_key != pkey:
+            with torch.cuda.device(self.zplanes.device):
+                if not lib.bqq_device_supported():
+                    raise RuntimeError('bqq_b200: the current GPU is not an sm_100 device')
+            st.dims = self._dims()
+            if (self.zplanes.numel() != lib.bqq_zplane_words(st.dims) or self.yplanes.numel() != lib.bqq_yplane_words(st.dims)
+                    or self.zplanes.dtype != torch.int32 or self.yplanes.dtype != torch.int32):
+                raise RuntimeError('bqq_b200: plane buffers do not match the layer geometry')
+            st.zplanes, st.yplanes = self.zplanes.contiguous(), self.yplanes.contiguous()
+            st.ysum = st.zsum = None
+            st.plane_key = pkey
+        return st
+
+    def get_weight(self, dtype=torch.float32):
+        if not self.zplanes.is_cuda or dtype not in _DTYPE_CODE:
+            raise RuntimeError('bqq_b200: PlaneBinaryQuadratic.get_weight needs the module on an sm_100 GPU '
+                               'and an fp32/bf16/fp16 dtype')
+        return self._weight_gpu(dtype)
+
+    def unpack_planes(self):
+        """Bit planes back to bool Y [bw,rw,cw,P,r], Z [bw,rw,cw,r,Q]."""
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        shape = (self.bit_width, self.row_width, self.col_width)
+        Y = torch.empty(shape + (self.y_row, self.inter_dimension), dtype=torch.uint8, device=device)
+        Z = torch.empty(shape + (self.inter_dimension, self.z_col), dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            check(lib.bqq_unpack_planes(st.zplanes.data_ptr(), st.yplanes.data_ptr(), st.dims, Y.data_ptr(),
+                                        Z.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+                  'bqq_unpack_planes')
+        return Y.bool(), Z.bool()
+
+
 def pack_binaryquadratic_model(model: nn.Module) -> nn.Module:
     """Replace every BinaryQuadratic by its packed twin (src/bqq_modules.py:435-442)."""
     for name, module in list(model.named_children()):
@@ -477,11 +573,14 @@ def get_matrices(patch_list, bit_width):
     return A, Y, Z
 
 
-def replace_linear_with_bqq(model: nn.Module, load_patches, bit_width: int, prefix: str = '') -> nn.Module:
+def replace_linear_with_bqq(model: nn.Module, load_patches, bit_width: int, prefix: str = '',
+                            planes_only: bool = False) -> nn.Module:
     """Walk the module tree and replace nn.Linear by BinaryQuadratic, skipping
     any name that contains 'head', as lm/build_bqq_model.py:79-112 does.
     `load_patches(weight_key)` returns the patch list of `<name>.weight` or None
-    (the reference reads it from its consolidated patch files)."""
+    (the reference reads it from its consolidated patch files).  With
+    `planes_only` the layers are PlaneBinaryQuadratic, packed patch by patch
+    without the dense Y / Z tensors."""
     for name, module in list(model.named_children()):
         full = f'{prefix}.{name}' if prefix else name
         if 'head' in full:
@@ -490,10 +589,14 @@ def replace_linear_with_bqq(model: nn.Module, load_patches, bit_width: int, pref
             patches = load_patches(f'{full}.weight')
             if not patches:
                 continue
-            A, Y, Z = get_matrices(patches, bit_width)
-            setattr(model, name, BinaryQuadratic(Y, Z, A, bias=module.bias))
+            if planes_only:
+                bias = module.bias.data.clone() if module.bias is not None else None
+                setattr(model, name, PlaneBinaryQuadratic.from_patches(patches, bit_width, bias=bias))
+            else:
+                A, Y, Z = get_matrices(patches, bit_width)
+                setattr(model, name, BinaryQuadratic(Y, Z, A, bias=module.bias))
         else:
-            replace_linear_with_bqq(module, load_patches, bit_width, prefix=full)
+            replace_linear_with_bqq(module, load_patches, bit_width, prefix=full, planes_only=planes_only)
     return model
 
 

@@ -248,6 +248,27 @@ int bqq_pack_planes_host(const uint8_t* Y_bool, const uint8_t* Z_bool, const Bqq
   return BQQ_OK;
 }
 
+int bqq_pack_patch_host(const uint8_t* mat1, const uint8_t* mat2, const BqqDims* dims, int bit, int i, int j,
+                        uint32_t* zplanes, uint32_t* yplanes) {
+  if (int rc = check_dims(dims)) return rc;
+  if (!mat1 || !mat2 || !zplanes || !yplanes) return BQQ_ERR_NULL;
+  if (bit < 0 || bit >= dims->bw || i < 0 || i >= dims->rw || j < 0 || j >= dims->cw) return BQQ_ERR_BAD_SHAPE;
+  Geom g(*dims);
+  int pos;
+  // replace the patch's bits (clear, then set), so a later entry for the same (bit, i, j) wins as in get_matrices
+  for (int p = 0; p < g.P; ++p)
+    for (int k = 0; k < g.r; ++k) {
+      uint32_t& w = yplanes[g.y_word(bit, i, j, p, k, &pos)];
+      w = (w & ~(1u << pos)) | ((mat1[(size_t)p * g.r + k] ? 1u : 0u) << pos);
+    }
+  for (int k = 0; k < g.r; ++k)
+    for (int q = 0; q < g.Q; ++q) {
+      uint32_t& w = zplanes[g.z_word(bit, i, j, k, q, &pos)];
+      w = (w & ~(1u << pos)) | ((mat2[(size_t)k * g.Q + q] ? 1u : 0u) << pos);
+    }
+  return BQQ_OK;
+}
+
 int bqq_unpack_planes_host(const uint32_t* zplanes, const uint32_t* yplanes, const BqqDims* dims,
                            uint8_t* Y_bool, uint8_t* Z_bool) {
   int rc = check_dims(dims);

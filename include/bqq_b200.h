@@ -123,6 +123,17 @@ int bqq_pack_planes_host(const uint8_t* Y_bool, const uint8_t* Z_bool, const Bqq
 int bqq_unpack_planes_host(const uint32_t* zplanes, const uint32_t* yplanes, const BqqDims* dims,
                            uint8_t* Y_bool, uint8_t* Z_bool);
 /*
+ * One patch straight into HOST planes: mat1 [P,r] and mat2 [r,Q] (one byte per
+ * element, non-zero = 1) of bit layer `bit`, row patch i, col patch j replace that
+ * patch's bits in zplanes / yplanes (zero-initialised by the caller, sized by
+ * bqq_zplane_words / bqq_yplane_words).  Lets a loader stream the reference's
+ * patch files ({patch_row, patch_col, coeff, mat1, mat2, bit_idx} dicts, gathered
+ * into dense tensors by get_matrices, src/bqq_modules.py:485-507) into planes
+ * without the dense Y/Z intermediate (32 times the planes' size as bytes).
+ */
+int bqq_pack_patch_host(const uint8_t* mat1, const uint8_t* mat2, const BqqDims* dims, int bit, int i, int j,
+                        uint32_t* zplanes, uint32_t* yplanes);
+/*
  * Re-pack the reference's own uint8 checkpoints (PackedBinaryQuadratic buffers
  * Y_packed [bw,rw,cw,P,ceil(r/8)], Z_packed [bw,rw,cw,Q,ceil(r/8)], big-endian,
  * Z transposed; src/bqq_modules.py:70-74) into bit planes (ysum/zsum optional).

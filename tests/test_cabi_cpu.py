@@ -144,3 +144,47 @@ def test_module_api_surface_on_cpu():
         bq(torch.randn(1, 128))
     with pytest.raises(RuntimeError, match='inference-only'):
         bq(torch.randn(1, 128))
+
+
+def _patch_list(bw_total, rw, cw, P, Q, r, seed):
+    """Patch dicts as the reference's consolidated files hold them, in a shuffled order."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    patches = []
+    for b in range(bw_total):
+        for i in range(rw):
+            for j in range(cw):
+                patches.append({'patch_row': i, 'patch_col': j, 'bit_idx': b,
+                                'coeff': torch.randn(4, generator=g) * 0.02,
+                                'mat1': (torch.rand(P, r, generator=g) > 0.5).float(),
+                                'mat2': (torch.rand(r, Q, generator=g) > 0.5).float()})
+    order = torch.randperm(len(patches), generator=g).tolist()
+    return [patches[k] for k in order]
+
+
+@pytest.mark.parametrize('geom', [(3, 3, 5, 32, 32, 32), (2, 2, 3, 64, 48, 20)])
+def test_patches_straight_into_planes(geom):
+    """PlaneBinaryQuadratic.from_patches (bqq_pack_patch_host, one patch at a time) builds the planes and
+    coefficients that get_matrices + the whole-layer packer build, including the skipping of
+    bit_idx >= bit_width and last-entry-wins for repeated patches."""
+    import torch
+    from bqq_b200.bqq_modules import PlaneBinaryQuadratic, get_matrices
+    bw_total, rw, cw, P, Q, r = geom
+    bit_width = bw_total - 1                                  # the last bit layer of the file is ignored
+    patches = _patch_list(bw_total, rw, cw, P, Q, r, seed=3)
+    dup = dict(patches[0])
+    dup['mat1'] = 1.0 - dup['mat1']
+    dup['coeff'] = dup['coeff'] * 2
+    patches.append(dup)                                       # repeated (bit, row, col): the later entry wins
+    layer = PlaneBinaryQuadratic.from_patches(patches, bit_width)
+    A, Y, Z = get_matrices(patches, bit_width)
+    zp, yp, _, _ = O.pack_planes_u32(Y.numpy() > 0.5, Z.numpy() > 0.5)
+    assert np.array_equal(layer.zplanes.numpy().view(np.uint32), zp.reshape(-1))
+    assert np.array_equal(layer.yplanes.numpy().view(np.uint32), yp.reshape(-1))
+    a, b, c, d = O.split_coefficients(A.numpy())
+    for name, want in zip('abcd', (a, b, c, d)):
+        assert np.array_equal(getattr(layer, name).detach().numpy(), want), name
+    assert (layer.bit_width, layer.row_width, layer.col_width, layer.y_row, layer.z_col, layer.inter_dimension) == \
+        (bit_width, rw, cw, P, Q, r)
+    sd = layer.state_dict()
+    assert list(sd) == ['a', 'b', 'c', 'd', 'zplanes', 'yplanes']

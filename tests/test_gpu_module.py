@@ -178,3 +178,27 @@ def test_forward_host_with_pageable_buffers():
         bq.forward_host(xh, out)
         torch.cuda.current_stream().synchronize()
         assert torch.equal(out.cuda(), _fwd(bq, xh.cuda()))
+
+
+def test_plane_layer_from_patches_equals_dense_route():
+    """Patch files packed patch by patch (no dense Y / Z) give the forward and the weight of
+    get_matrices + BinaryQuadratic bit for bit."""
+    from bqq_b200.bqq_modules import BinaryQuadratic, PlaneBinaryQuadratic, get_matrices
+    from tests.test_cabi_cpu import _patch_list
+    patches = _patch_list(3, 4, 6, 32, 32, 32, seed=9)
+    A, Y, Z = get_matrices(patches, 3)
+    dense = BinaryQuadratic(Y, Z, A).cuda()
+    planes = PlaneBinaryQuadratic.from_patches(patches, 3).cuda()
+    g = torch.Generator().manual_seed(4)
+    for M, dt in ((1, torch.bfloat16), (7, torch.float32), (33, torch.float16)):
+        X = torch.randn(M, 6 * 32, generator=g).to(dt).cuda()
+        assert torch.equal(_fwd(planes, X), _fwd(dense, X))
+    assert torch.equal(planes.get_weight(torch.float32), dense.get_weight(torch.float32))
+    Yb, Zb = planes.unpack_planes()
+    assert torch.equal(Yb, dense.Y) and torch.equal(Zb, dense.Z)
+    buf = io.BytesIO()
+    torch.save(planes, buf)
+    buf.seek(0)
+    again = torch.load(buf, weights_only=False)
+    X = torch.randn(2, 6 * 32, generator=g).cuda()
+    assert torch.equal(_fwd(again, X), _fwd(dense, X))
