@@ -11,8 +11,8 @@ KV cache.
 
 Only the BinaryQuadratic layers are the product here; normalisation, rotary embedding,
 attention and the dense lm_head are plain torch ops (plumbing).  With world > 1 the layers are
-column-parallel (bqq_b200/sharded.py): q/k/v are sharded by heads so attention runs on local
-heads, gate/up share one sharding so SwiGLU is local, o_proj and down_proj are row-patch
+column-parallel (bqq_b200/sharded.py): q/k/v (one stacked layer) are sharded by heads so attention
+runs on local heads, gate/up (one stacked layer) share one sharding so SwiGLU is local, o_proj and down_proj are row-patch
 sharded; four gathers per layer, all without reductions.  With a PeerGatherGroup the gathers are the
 library's peer-to-peer stores (o_proj and down_proj send their row patches from the decode kernel's
 epilogue, the attention output and the SwiGLU product go through the gather kernel); results too large
@@ -75,13 +75,12 @@ class DecoderLayer(nn.Module):
         if cfg.heads % world or (cfg.kv_heads % world and world % cfg.kv_heads):
             raise ValueError('heads must divide evenly over the ranks')
         h = cfg.hidden
-        # each rank builds only its own row-patch shard (a shard is a layer with fewer row patches)
-        self.q_proj = random_bq(self.local_heads * hd, h, cfg, device, gen)
-        self.k_proj = random_bq(self.local_kv * hd, h, cfg, device, gen)
-        self.v_proj = random_bq(self.local_kv * hd, h, cfg, device, gen)
+        # each rank builds only its own row-patch shard (a shard is a layer with fewer row patches).
+        # q, k and v share their input, so their row patches are stacked into one layer (one launch
+        # instead of three); likewise gate and up.  Row patches are independent, so this is the same math.
+        self.qkv_proj = random_bq((self.local_heads + 2 * self.local_kv) * hd, h, cfg, device, gen)
         self.o_proj = random_bq(h // world, h, cfg, device, gen)
-        self.gate_proj = random_bq(cfg.intermediate // world, h, cfg, device, gen)
-        self.up_proj = random_bq(cfg.intermediate // world, h, cfg, device, gen)
+        self.gate_up_proj = random_bq(2 * (cfg.intermediate // world), h, cfg, device, gen)
         self.down_proj = random_bq(h // world, cfg.intermediate, cfg, device, gen)
         self.norm1 = nn.Parameter(torch.ones(h, device=device, dtype=torch.bfloat16))
         self.norm2 = nn.Parameter(torch.ones(h, device=device, dtype=torch.bfloat16))
@@ -105,7 +104,7 @@ class DecoderLayer(nn.Module):
             return proj.forward_gathered(x, self.peer)
         return self._gather(proj(x))
 
-    def forward(self, x, k_cache, v_cache, pos, cos, sin, mask=None):
+    def forward(self, x, k_cache, v_cache, pos, rot, mask=None):
         """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim].
 
         Prefill: `pos` is a Python int, positions pos..pos+T are written and attention is causal over
@@ -115,10 +114,12 @@ class DecoderLayer(nn.Module):
         B, T, _ = x.shape
         hd = cfg.head_dim
         hx = F.rms_norm(x, (cfg.hidden,), self.norm1, 1e-5)
-        q = self.q_proj(hx).view(B, T, self.local_heads, hd).transpose(1, 2)
-        k = self.k_proj(hx).view(B, T, self.local_kv, hd).transpose(1, 2)
-        v = self.v_proj(hx).view(B, T, self.local_kv, hd).transpose(1, 2)
-        q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+        lh, lkv = self.local_heads, self.local_kv
+        qkv = self.qkv_proj(hx).view(B, T, lh + 2 * lkv, hd)
+        qk = _rope(qkv[:, :, :lh + lkv], rot)                        # rotary embedding on q and k heads at once
+        q = qk[:, :, :lh].transpose(1, 2)
+        k = qk[:, :, lh:].transpose(1, 2)
+        v = qkv[:, :, lh + lkv:].transpose(1, 2)
         if mask is None:
             k_cache[:, :, pos:pos + T] = k
             v_cache[:, :, pos:pos + T] = v
@@ -131,15 +132,17 @@ class DecoderLayer(nn.Module):
         att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
         x = x + self._proj_gathered(self.o_proj, att)                                       # gather 2
         hx = F.rms_norm(x, (cfg.hidden,), self.norm2, 1e-5)
-        act = F.silu(self.gate_proj(hx)) * self.up_proj(hx)
+        gu = self.gate_up_proj(hx)
+        n = gu.shape[-1] // 2
+        act = F.silu(gu[..., :n]) * gu[..., n:]
         act = self._gather(act)                                                             # gather 3
         return x + self._proj_gathered(self.down_proj, act)                                 # gather 4
 
 
-def _rope(x, cos, sin):
-    x1, x2 = x[..., ::2], x[..., 1::2]
-    out = torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1)
-    return out.flatten(-2).to(x.dtype)
+def _rope(x, rot):
+    """x [B, T, heads, head_dim], rot complex [T, head_dim/2]: rotate the pairs (x[2i], x[2i+1])."""
+    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+    return torch.view_as_real(xc * rot[None, :, None, :]).flatten(-2).to(x.dtype)
 
 
 class DecoderStack(nn.Module):
@@ -156,7 +159,7 @@ class DecoderStack(nn.Module):
                         * (1.0 / math.sqrt(cfg.hidden))).to(torch.bfloat16)
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float() / cfg.head_dim))
         ang = torch.arange(cfg.max_seq, device=device).float()[:, None] * inv[None, :]
-        self.cos, self.sin = ang.cos(), ang.sin()
+        self.rot = torch.polar(torch.ones_like(ang), ang)           # e^{i * position * frequency}, [max_seq, head_dim/2]
 
     def bqq_bytes_per_token(self) -> int:
         """Packed bits + fp32 coefficients streamed per decoded token on this rank."""
@@ -190,9 +193,9 @@ class DecoderStack(nn.Module):
         """ids [B, T] prompt -> first generated token ids [B]; fills cache positions 0..T."""
         x = self.embed[ids]
         T = ids.shape[1]
-        cos, sin = self.cos[:T], self.sin[:T]
+        rot = self.rot[:T]
         for li, layer in enumerate(self.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], 0, cos, sin)
+            x = layer(x, cache[li, 0], cache[li, 1], 0, rot)
         return self._head(x[:, -1])
 
     @torch.no_grad()
@@ -200,8 +203,8 @@ class DecoderStack(nn.Module):
         """One greedy decode step with static shapes (CUDA-graph capturable).
         ids [B] int64, pos 1-element int64 device tensor; returns next ids [B]."""
         x = self.embed[ids].unsqueeze(1)
-        cos, sin = self.cos.index_select(0, pos), self.sin.index_select(0, pos)
+        rot = self.rot.index_select(0, pos)
         mask = (torch.arange(self.cfg.max_seq, device=self.device) <= pos).view(1, 1, 1, -1)
         for li, layer in enumerate(self.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], pos, cos, sin, mask)
+            x = layer(x, cache[li, 0], cache[li, 1], pos, rot, mask)
         return self._head(x[:, -1])
