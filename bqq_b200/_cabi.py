@@ -20,7 +20,7 @@ EXPORTS = [
     'bqq_zplane_words', 'bqq_yplane_words', 'bqq_algorithmic_bytes',
     'bqq_pack_planes', 'bqq_unpack_planes', 'bqq_pack_planes_host', 'bqq_unpack_planes_host', 'bqq_pack_patch_host',
     'bqq_repack_u8_planes',
-    'bqq_decode_workspace_bytes', 'bqq_forward_decode',
+    'bqq_decode_workspace_bytes', 'bqq_forward_decode', 'bqq_forward_decode_fused',
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
     'bqq_decode_launches', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
@@ -38,6 +38,14 @@ class BqqLayer(C.Structure):
     _fields_ = [('dims', BqqDims), ('zplanes', C.c_void_p), ('yplanes', C.c_void_p),
                 ('a', C.c_void_p), ('b', C.c_void_p), ('c', C.c_void_p), ('d', C.c_void_p),
                 ('bias', C.c_void_p), ('coef_dtype', C.c_int32), ('bias_dtype', C.c_int32)]
+
+
+PRO_NONE, PRO_RMSNORM, PRO_SWIGLU = 0, 1, 2
+
+
+class BqqFusion(C.Structure):
+    _fields_ = [('prologue', C.c_int32), ('norm_dtype', C.c_int32), ('norm_weight', C.c_void_p), ('eps', C.c_float),
+                ('residual_dtype', C.c_int32), ('residual', C.c_void_p), ('ld_residual', C.c_int64)]
 
 
 MAX_PEERS = 8
@@ -73,6 +81,7 @@ def _load():
         'bqq_prefill_workspace_bytes': (sz, [dp, i32]),
         'bqq_forward_workspace_bytes': (sz, [dp, i32]),
         'bqq_forward_decode': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
+        'bqq_forward_decode_fused': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, C.POINTER(BqqFusion), vp, sz, vp]),
         'bqq_forward_prefill': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_forward': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_reconstruct_weight': (i32, [lp, vp, i32, f32, vp]),

@@ -15,6 +15,8 @@ and no CPU fallback: a module whose buffers are not on an sm_100 GPU raises.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 import torch.nn as nn
 
@@ -187,6 +189,70 @@ class _BqqForwardMixin:
                 check(lib.bqq_forward_prefill(layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(),
                                               code, y.stride(0), ws.data_ptr(), ws.numel(), stream),
                       'bqq_forward_prefill')
+        return y.reshape(*X.shape[:-1], out_f)
+
+    def forward_fused(self, X, rms_weight=None, eps: float = 1e-5, swiglu: bool = False, residual=None):
+        """Forward with the neighbouring element-wise operations of a decoder block folded into the
+        kernels (bqq_forward_decode_fused):
+
+            rms_weight:  the layer sees  rms_norm(X, weight=rms_weight, eps)
+            swiglu:      X is [..., 2*in] = [gate | up]; the layer sees  silu(gate) * up
+            residual:    [..., out] added to the output (pass the tensor the result replaces)
+
+        The prologue runs in fp32 on the unrounded values.  Up to 16 rows this is one decode call; larger
+        batches apply the same operations with torch ops and call forward()."""
+        self._check_inference_only(X)
+        if rms_weight is not None and swiglu:
+            raise RuntimeError('bqq_b200: rms_weight and swiglu cannot be combined')
+        in_f = self.col_width * self.z_col
+        out_f = self.row_width * self.y_row
+        width = 2 * in_f if swiglu else in_f
+        if X.shape[-1] != width:
+            raise RuntimeError(f'bqq_b200: last dim of X is {X.shape[-1]}, expected {width}')
+        M = X.numel() // width
+        if M > _cabi.DECODE_MAX_M or M == 0 or X.dtype not in _DTYPE_CODE:
+            H = X
+            if rms_weight is not None:
+                H = torch.nn.functional.rms_norm(X, (in_f,), rms_weight, eps)
+            elif swiglu:
+                H = torch.nn.functional.silu(X[..., :in_f]) * X[..., in_f:]
+            Yo = self.forward(H)
+            return Yo if residual is None else residual + Yo
+        st = self._ensure_packed()
+        device = st.zplanes.device
+        X = X.to(device)
+        x2 = X.reshape(-1, width)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = torch.empty((M, out_f), dtype=X.dtype, device=device)
+        fusion = _cabi.BqqFusion()
+        keep = []
+        if rms_weight is not None:
+            w = rms_weight.detach()
+            _require_cuda(w, 'the normalisation weight')
+            if w.dtype not in _DTYPE_CODE or w.numel() != in_f:
+                raise RuntimeError('bqq_b200: rms_weight must be an fp32/bf16/fp16 vector of in_features elements')
+            w = w.contiguous()
+            keep.append(w)
+            fusion.prologue, fusion.norm_weight, fusion.norm_dtype, fusion.eps = (
+                _cabi.PRO_RMSNORM, w.data_ptr(), _DTYPE_CODE[w.dtype], float(eps))
+        elif swiglu:
+            fusion.prologue = _cabi.PRO_SWIGLU
+        if residual is not None:
+            r2 = residual.reshape(-1, out_f)
+            if (not residual.is_cuda or r2.shape[0] != M or r2.stride(-1) != 1 or residual.dtype not in _DTYPE_CODE):
+                raise RuntimeError('bqq_b200: residual must be a CUDA tensor [..., out_features] with unit inner stride')
+            keep.append(r2)
+            fusion.residual, fusion.ld_residual, fusion.residual_dtype = (
+                r2.data_ptr(), r2.stride(0), _DTYPE_CODE[residual.dtype])
+        code = _DTYPE_CODE[X.dtype]
+        layer = self._layer(st)
+        with torch.cuda.device(device):
+            ws = _workspace(device, 'decode', lib.bqq_decode_workspace_bytes(st.dims, M))
+            check(lib.bqq_forward_decode_fused(layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(), code,
+                                               y.stride(0), C.byref(fusion), ws.data_ptr(), ws.numel(),
+                                               torch.cuda.current_stream(device).cuda_stream),
+                  'bqq_forward_decode_fused')
         return y.reshape(*X.shape[:-1], out_f)
 
     def forward_gathered(self, X, peer, out=None):

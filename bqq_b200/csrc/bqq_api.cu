@@ -27,14 +27,24 @@ static int check_io(const BqqLayer* L, const void* x, int x_dtype, int M, int64_
 
 // bqq_forward_decode, optionally with the peer stores of bqq_forward_decode_gathered (not exported in the header)
 int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
-                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer) {
+                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
+                            const BqqFusion* fusion = nullptr) {
   int rc = check_layer(layer);
   if (rc) return rc;
   rc = check_io(layer, x, x_dtype, M, ldx, y, y_dtype, ldy);
   if (rc) return rc;
   if (M > BQQ_DECODE_MAX_M) return BQQ_ERR_UNSUPPORTED;
+  if (fusion) {
+    Geom g(layer->dims);
+    if (fusion->prologue < BQQ_PRO_NONE || fusion->prologue > BQQ_PRO_SWIGLU) return BQQ_ERR_BAD_SHAPE;
+    if (fusion->prologue == BQQ_PRO_RMSNORM && (!fusion->norm_weight || !dtype_size(fusion->norm_dtype)))
+      return fusion->norm_weight ? BQQ_ERR_DTYPE : BQQ_ERR_NULL;
+    if (fusion->prologue == BQQ_PRO_SWIGLU && ldx < 2 * (int64_t)g.in_features()) return BQQ_ERR_BAD_SHAPE;
+    if (fusion->residual && (!dtype_size(fusion->residual_dtype) || fusion->ld_residual < g.out_features()))
+      return dtype_size(fusion->residual_dtype) ? BQQ_ERR_BAD_SHAPE : BQQ_ERR_DTYPE;
+  }
   return decode_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
-                       (cudaStream_t)stream, peer);
+                       (cudaStream_t)stream, peer, fusion);
 }
 
 extern "C" {
@@ -78,6 +88,13 @@ size_t bqq_decode_workspace_bytes(const BqqDims* dims, int M) {
 int bqq_forward_decode(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                        int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
   return bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream, nullptr);
+}
+
+int bqq_forward_decode_fused(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
+                             int y_dtype, int64_t ldy, const BqqFusion* fusion, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  return bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream, nullptr,
+                                 fusion);
 }
 
 size_t bqq_prefill_workspace_bytes(const BqqDims* dims, int M) {

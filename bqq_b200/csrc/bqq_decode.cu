@@ -63,7 +63,8 @@ size_t decode_workspace_bytes(const BqqDims* dims, int M) {
 }
 
 int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t ldx, void* y,
-                  int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t st, const BqqPeerGroup* peer) {
+                  int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t st, const BqqPeerGroup* peer,
+                  const BqqFusion* fusion) {
   Geom g(L->dims);
   DecodePlan pl = make_decode_plan(g, M);
   if (pl.variant < 0) return BQQ_ERR_UNSUPPORTED;
@@ -97,6 +98,16 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
   p.coef_vec = (L->coef_dtype == BQQ_F32 && g.cw % 4 == 0 && (((uintptr_t)L->a | (uintptr_t)L->b |
                                                                  (uintptr_t)L->c | (uintptr_t)L->d) & 15) == 0)
                    ? 1 : 0;
+  p.norm_w = p.res = nullptr;
+  p.ld_res = 0;
+  p.pro_mode = BQQ_PRO_NONE;
+  p.norm_dtype = p.res_dtype = 0;
+  p.eps = 0.f;
+  if (fusion) {
+    p.pro_mode = fusion->prologue;
+    p.norm_w = fusion->norm_weight; p.norm_dtype = fusion->norm_dtype; p.eps = fusion->eps;
+    p.res = fusion->residual; p.ld_res = fusion->ld_residual; p.res_dtype = fusion->residual_dtype;
+  }
   for (int q = 0; q < BQQ_MAX_PEERS; ++q) p.peer_regions[q] = nullptr;
   p.peer_world = p.peer_rank = p.peer_row_words = 0;
   p.peer_half = 0;

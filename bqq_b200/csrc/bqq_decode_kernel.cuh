@@ -77,6 +77,12 @@ struct DecodeParams {
   int PTg, QTg, RTg;       // 32-blocks of the planes as packed
   int JG, NS;
   int sgw, nchunks, mtiles, bpc;
+  // optional fused prologue (what is applied to x on the way in) and residual added to the outputs
+  const void* norm_w;
+  const void* res;
+  int64_t ld_res;
+  int pro_mode, norm_dtype, res_dtype;
+  float eps;
   // optional peer-to-peer send of the outputs (row-patch shards; all zero when unused): the regions of
   // every rank as mapped here, this rank, words of one local output row, bytes of one slot half
   uint8_t* peer_regions[BQQ_MAX_PEERS];
@@ -159,8 +165,40 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // (row, col patch) pair per 8 lanes.  `live` pairs read x[m, j*Q ...]; the others write zeros.
 // Digits go to words[] at the pair's place (M tile `mtile`, row `beta` inside it), statistics to
 // index `stat` of xscale / xsum / xl1.  Every lane of the warp must call it (shuffles).
+// Where the activation comes from, and what is applied to it on the way in (BqqFusion::prologue):
+// nothing, RMS normalisation (x * inv_rms * w[n]; inv_rms of the row is computed by the caller of
+// xprep_pair), or SwiGLU (silu(x[n]) * x[n + n_in], x holding [gate | up] rows of 2 * n_in elements).
+struct XSource {
+  const void* x;
+  const void* w;
+  int64_t ld;
+  int dtype, w_dtype, mode, n_in;
+  float eps;
+};
+__device__ __forceinline__ float load_x(const XSource& s, int m, int n, float inv_rms) {
+  float v = load_as_float(s.x, (size_t)m * s.ld + n, s.dtype);
+  if (s.mode == BQQ_PRO_RMSNORM) {
+    v = v * inv_rms * load_as_float(s.w, n, s.w_dtype);
+  } else if (s.mode == BQQ_PRO_SWIGLU) {
+    const float u = load_as_float(s.x, (size_t)m * s.ld + s.n_in + n, s.dtype);
+    v = v / (1.f + __expf(-v)) * u;
+  }
+  return v;
+}
+// Sum of squares of row m over this thread's share of the columns (threads tid, tid + n, ...).
+__device__ __forceinline__ float row_sumsq_share(const XSource& s, int m, int tid, int nthreads) {
+  float acc = 0.f;
+  for (int n = tid; n < s.n_in; n += nthreads) {
+    const float v = load_as_float(s.x, (size_t)m * s.ld + n, s.dtype);
+    acc = fmaf(v, v, acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;                                       // the warp's share, in every lane
+}
+
 template <int QT>
-__device__ __forceinline__ void xprep_pair(const void* __restrict__ x, int x_dtype, int64_t ldx, int Q, int NB, int JG,
+__device__ __forceinline__ void xprep_pair(const XSource& xs, float inv_rms, int Q, int NB, int JG,
                                            bool write, bool live, int m, int j, int mtile, int beta, int sub8,
                                            uint32_t* __restrict__ words, float* __restrict__ xscale,
                                            float* __restrict__ xsum, float* __restrict__ xl1, int stat) {
@@ -169,7 +207,7 @@ __device__ __forceinline__ void xprep_pair(const void* __restrict__ x, int x_dty
 #pragma unroll
   for (int e = 0; e < 4 * QT; ++e) {
     const int q = sub8 * 4 * QT + e;
-    v[e] = (live && q < Q) ? load_as_float(x, (size_t)m * ldx + (size_t)j * Q + q, x_dtype) : 0.f;
+    v[e] = (live && q < Q) ? load_x(xs, m, j * Q + q, inv_rms) : 0.f;
     amax = fmaxf(amax, fabsf(v[e]));
     sum += v[e];
     l1 += fabsf(v[e]);
@@ -208,7 +246,7 @@ __device__ __forceinline__ void xprep_pair(const void* __restrict__ x, int x_dty
 
 template <int QT>
 __global__ void __launch_bounds__(128)
-bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int cw, int Q, int Mp, int cwp, int NB,
+bqq_xprep_kernel(const XSource xs, int M, int cw, int Q, int cwp, int NB,
                  uint8_t* __restrict__ xdig, float* __restrict__ xscale, float* __restrict__ xsum,
                  float* __restrict__ xl1) {
   // the decode kernel of this layer may start now: it first streams its weight planes and only
@@ -217,12 +255,19 @@ bqq_xprep_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, in
   // writing the workspace.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int pairs = Mp * cwp;
-  const int pair = (blockIdx.x * 128 + threadIdx.x) >> 3;
-  const bool inside = pair < pairs;
-  const int m = inside ? pair / cwp : 0, j = inside ? pair % cwp : 0;
-  xprep_pair<QT>(x, x_dtype, ldx, Q, NB, cwp / kGroup, inside, inside && m < M && j < cw, m, j, m / NB, m % NB,
-                 threadIdx.x & 7, reinterpret_cast<uint32_t*>(xdig), xscale, xsum, xl1, pair);
+  const int m = blockIdx.y;                         // row of X (rows >= M are written as zeros)
+  float inv_rms = 1.f;
+  if (xs.mode == BQQ_PRO_RMSNORM) {                 // every block sums its row's squares itself (a few KB from L2)
+    __shared__ float part[4];
+    const float w = m < M ? row_sumsq_share(xs, m, threadIdx.x, 128) : 0.f;
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = w;
+    __syncthreads();
+    inv_rms = rsqrtf((part[0] + part[1] + part[2] + part[3]) / (float)xs.n_in + xs.eps);
+  }
+  const int j = (blockIdx.x * 128 + threadIdx.x) >> 3;
+  const bool inside = j < cwp;
+  xprep_pair<QT>(xs, inv_rms, Q, NB, cwp / kGroup, inside, inside && m < M && j < cw, m, inside ? j : 0, m / NB, m % NB,
+                 threadIdx.x & 7, reinterpret_cast<uint32_t*>(xdig), xscale, xsum, xl1, m * cwp + j);
 }
 
 // Final output of one lane (row `row` of X, local output column `o`) also travels to every rank of a
@@ -351,8 +396,19 @@ bqq_decode_kernel(const DecodeParams p) {
     // x and the workspace belong to earlier kernels of the stream until they have finished.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     float* st = const_cast<float*>(xstat);
+    const XSource xs = {p.x, p.norm_w, p.ldx, p.x_dtype, p.norm_dtype, p.pro_mode, p.cw * p.Q, p.eps};
+    float inv_rms = 1.f;
+    if (p.pro_mode == BQQ_PRO_RMSNORM) {              // the CTA reads its row of x anyway: sum the squares first
+      const float w = m0 < p.M ? row_sumsq_share(xs, m0, tid, kDT * bpc) : 0.f;
+      if (lane == 0) red[warp] = w;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w2 = 0; w2 < kDW * bpc; ++w2) tot += red[w2];
+      inv_rms = rsqrtf(tot / (float)xs.n_in + p.eps);
+      __syncthreads();                               // red is reused for the warps' sums at the end
+    }
     for (int pair = tid >> 3; pair < nsg * kGroup; pair += (kDT * bpc) >> 3)
-      xprep_pair<QT>(p.x, p.x_dtype, p.ldx, p.Q, NB, nsg, true, pair < p.cw && m0 < p.M, m0, pair, 0, 0, tid & 7,
+      xprep_pair<QT>(xs, inv_rms, p.Q, NB, nsg, true, pair < p.cw && m0 < p.M, m0, pair, 0, 0, tid & 7,
                      reinterpret_cast<uint32_t*>(sm + L.xres), st, st + nsg * 4, st + nsg * 8, pair);
     __syncthreads();
   } else {
@@ -677,6 +733,7 @@ bqq_decode_kernel(const DecodeParams p) {
       const int o = i * p.P + pp;
       if (valid) {
         if (p.bias) v += load_as_float(p.bias, o, p.bias_dtype);
+        if (p.res) v += load_as_float(p.res, (size_t)(m0 + beta) * p.ld_res + o, p.res_dtype);
         store_from_float(p.y, (size_t)(m0 + beta) * p.ldy + o, p.y_dtype, v);
       }
       if (p.peer_world) peer_send(p, valid, m0 + beta, o, v, lane);
@@ -709,6 +766,7 @@ bqq_decode_kernel(const DecodeParams p) {
       for (int sp = 0; sp < nparts; ++sp)
         v += __ldcg(p.partial + ((size_t)sp * mrows + m0 + beta) * out_stride + (size_t)i * PP + pp);
       if (p.bias) v += load_as_float(p.bias, o, p.bias_dtype);
+      if (p.res) v += load_as_float(p.res, (size_t)(m0 + beta) * p.ld_res + o, p.res_dtype);
       store_from_float(p.y, (size_t)(m0 + beta) * p.ldy + o, p.y_dtype, v);
     }
     if (p.peer_world) peer_send(p, valid, m0 + beta, o, v, lane);
@@ -733,14 +791,14 @@ static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cu
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   if (!merged) {
-    const int pairs = p.Mp * p.cwp;
+    const XSource xs = {p.x, p.norm_w, p.ldx, p.x_dtype, p.norm_dtype, p.pro_mode, p.cw * p.Q, p.eps};
     cudaLaunchConfig_t xc = {};
-    xc.gridDim = dim3((pairs * 8 + 127) / 128);
+    xc.gridDim = dim3((p.cwp * 8 + 127) / 128, p.Mp);
     xc.blockDim = dim3(128);
     xc.stream = st;
     xc.attrs = attr;
     xc.numAttrs = 1;
-    if (cudaLaunchKernelEx(&xc, bqq_xprep_kernel<QT>, p.x, p.x_dtype, p.ldx, p.M, p.cw, p.Q, p.Mp, p.cwp, (int)NB,
+    if (cudaLaunchKernelEx(&xc, bqq_xprep_kernel<QT>, xs, p.M, p.cw, p.Q, p.cwp, (int)NB,
                            const_cast<uint8_t*>(p.xdig), const_cast<float*>(p.xscale), const_cast<float*>(p.xsum),
                            const_cast<float*>(p.xl1)) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   }

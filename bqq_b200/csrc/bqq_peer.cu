@@ -22,7 +22,8 @@
 
 // bqq_forward_decode with the peer group handed through to the kernel (bqq_api.cu)
 int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
-                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer);
+                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
+                            const BqqFusion* fusion = nullptr);
 
 namespace bqq {
 

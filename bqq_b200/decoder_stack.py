@@ -113,9 +113,13 @@ class DecoderLayer(nn.Module):
         cfg = self.cfg
         B, T, _ = x.shape
         hd = cfg.head_dim
-        hx = F.rms_norm(x, (cfg.hidden,), self.norm1, 1e-5)
         lh, lkv = self.local_heads, self.local_kv
-        qkv = self.qkv_proj(hx).view(B, T, lh + 2 * lkv, hd)
+        fused = self.world == 1          # normalisation, SwiGLU and residual adds folded into the layers' kernels
+        if fused:
+            qkv = self.qkv_proj.forward_fused(x, rms_weight=self.norm1, eps=1e-5)
+        else:
+            qkv = self.qkv_proj(F.rms_norm(x, (cfg.hidden,), self.norm1, 1e-5))
+        qkv = qkv.view(B, T, lh + 2 * lkv, hd)
         qk = _rope(qkv[:, :, :lh + lkv], rot)                        # rotary embedding on q and k heads at once
         q = qk[:, :, :lh].transpose(1, 2)
         k = qk[:, :, lh:].transpose(1, 2)
@@ -130,6 +134,10 @@ class DecoderLayer(nn.Module):
             v_cache.index_copy_(2, pos, v)
             att = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=mask, enable_gqa=True)
         att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
+        if fused:
+            x = self.o_proj.forward_fused(att, residual=x)
+            gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)
+            return self.down_proj.forward_fused(gu, swiglu=True, residual=x)
         x = x + self._proj_gathered(self.o_proj, att)                                       # gather 2
         hx = F.rms_norm(x, (cfg.hidden,), self.norm2, 1e-5)
         gu = self.gate_up_proj(hx)

@@ -183,6 +183,33 @@ int bqq_forward(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_
                 void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * bqq_forward_decode with the neighbouring element-wise operations of a decoder
+ * block folded in (the reference runs them as separate torch ops around the
+ * module; it has no counterpart).  prologue, applied to x as it is read:
+ *   BQQ_PRO_NONE     x as is;
+ *   BQQ_PRO_RMSNORM  x[m,n] * rsqrt(mean_n x[m,:]^2 + eps) * norm_weight[n];
+ *   BQQ_PRO_SWIGLU   silu(x[m,n]) * x[m, in + n]: x has rows [gate | up] of
+ *                    2*in elements (ldx >= 2*in).
+ * residual (may be NULL, may alias y): [M, out] added to the output before it is
+ * stored.  All prologue arithmetic is fp32.  fusion == NULL is bqq_forward_decode.
+ */
+#define BQQ_PRO_NONE    0
+#define BQQ_PRO_RMSNORM 1
+#define BQQ_PRO_SWIGLU  2
+typedef struct BqqFusion {
+  int32_t prologue;
+  int32_t norm_dtype;          /* element type of norm_weight */
+  const void* norm_weight;     /* [in], BQQ_PRO_RMSNORM only */
+  float eps;
+  int32_t residual_dtype;
+  const void* residual;
+  int64_t ld_residual;         /* row pitch of residual in elements */
+} BqqFusion;
+int bqq_forward_decode_fused(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
+                             void* y, int y_dtype, int64_t ldy, const BqqFusion* fusion,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Number of kernels one bqq_forward_decode call enqueues for this layer shape and
  * M (1 or 2: short single-chunk layers at M = 1 prepare x inside the decode
  * kernel, all others launch a preparation kernel first); negative BQQ_ERR_* for

@@ -182,3 +182,45 @@ def test_linearity_full_size():
         ref = O.forward(Y[:, i:i + 1].cpu().numpy(), Z[:, i:i + 1].cpu().numpy(), a, b, c, d, x1.cpu().numpy())
         got = y1[:, i * P:(i + 1) * P].cpu().numpy()
         assert np.abs(got - ref).max() < TOL_FP32 * scale
+
+
+@pytest.mark.parametrize('geom,M,dtype', [((2, 6, 5, 32, 32, 32), 1, torch.bfloat16),     # all bit layers per CTA
+                                          ((3, 4, 40, 32, 32, 32), 1, torch.float32),     # preparation kernel
+                                          ((2, 4, 6, 64, 64, 32), 5, torch.float16),
+                                          ((2, 3, 9, 32, 32, 32), 16, torch.bfloat16)])
+def test_fused_prologue_and_residual(geom, M, dtype):
+    """bqq_forward_decode_fused: RMS normalisation or SwiGLU applied to x on the way in, residual added on the
+    way out, against the fp32 oracle on the same (fp32) prologue arithmetic."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, P, Q, r = geom
+    Y, Z, A, bias, _ = synth_layer(bw, rw, cw, P, Q, r, M, seed=41, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    g = torch.Generator().manual_seed(7)
+    in_f, out_f = cw * Q, rw * P
+    w = (1.0 + 0.1 * torch.randn(in_f, generator=g)).to(dtype)
+    res = torch.randn(M, out_f, generator=g).to(dtype)
+    tol = TOL if dtype == torch.float32 else TOL + 2 ** -8
+
+    def oracle(H):
+        return oracle_forward_t(Y, Z, A, bias, H)
+
+    with torch.no_grad():
+        # RMS normalisation + residual
+        X = (3.0 * torch.randn(M, in_f, generator=g)).to(dtype)
+        got = bq.forward_fused(X.cuda(), rms_weight=w.cuda(), eps=1e-5, residual=res.cuda())
+        Xf = X.float()
+        H = Xf * torch.rsqrt(Xf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+        want = oracle(H) + res.float().numpy()
+        assert O.max_rel_err(got.float().cpu().numpy(), want) < tol
+        # SwiGLU, no residual
+        GU = torch.randn(M, 2 * in_f, generator=g).to(dtype)
+        got = bq.forward_fused(GU.cuda(), swiglu=True)
+        H = torch.nn.functional.silu(GU.float()[:, :in_f]) * GU.float()[:, in_f:]
+        assert O.max_rel_err(got.float().cpu().numpy(), oracle(H)) < tol
+        # residual alone
+        h = res.cuda().clone()
+        X = torch.randn(M, in_f, generator=g).to(dtype)
+        got = bq.forward_fused(X.cuda(), residual=h)
+        assert O.max_rel_err(got.float().cpu().numpy(), oracle(X.float()) + res.float().numpy()) < tol
+        # no fusion at all equals the plain forward bit for bit
+        assert torch.equal(bq.forward_fused(X.cuda()), bq(X.cuda()))
