@@ -1,5 +1,5 @@
 // Decode kernel (M <= 16 rows of X): the packed planes are streamed once and both
-// contractions run on the int8 tensor cores (mma.sync m16n8k32, u8 x s8 -> s32).
+// contractions run on the int8 tensor cores (mma.sync m16n8k32, u8 x s8 and u8 x u8 -> s32).
 //
 // Per (row patch i, col patch j, bit b) with coefficients (a,b,c,d):
 //   xsum = sum_q x[j,q];  t_k = sum_q Z[k,q] x[j,q];  u_k = a t_k + b xsum
@@ -13,8 +13,10 @@
 // 0 or 2^rr, so a bit costs 1/4 of a logic instruction to expand.  The power of
 // two is removed again when the s32 results are converted.
 // Real operand: x is quantised per col patch to 16-bit block fixed point (two s8
-// digits) by a small preparation kernel, u per warp to 24-bit fixed point (three s8
-// digits); digits occupy
+// digits) by a small preparation kernel or by the decode CTA itself, u per warp to
+// 23-bit fixed point (three unsigned base-256 digits of round(u / scale) + offset,
+// read off the bit pattern of one fused multiply-add; a fourth B column of ones
+// accumulates the row sums of Y that remove the offset again).  Digits occupy
 // separate B-operand columns, so the integer products are exact and the only
 // errors are the two roundings (about 2^-16 of the patch maximum of |x|).
 //
@@ -25,14 +27,17 @@
 // main loop; coefficients and x statistics of the chunk arrive by bulk copies on one
 // mbarrier.  The split never depends on the number of row patches, so a row shard of a
 // layer produces bit-identical outputs.  CTA partial sums go to scratch; the last
-// CTA of a row patch adds them in a fixed order, adds bias and converts to the
-// output type.
+// CTA of a row patch adds them in a fixed order, adds bias (and an optional residual)
+// and converts to the output type.  Short single-chunk layers at M = 1 instead give
+// one CTA all bit layers of a row patch (template flag MB): it prepares x itself and
+// its sums never leave shared memory.
 #pragma once
 #include "bqq_async.cuh"
 #include "bqq_common.cuh"
 
 namespace bqq {
 
+// tunables (measured on B200): ring slots for slot sizes of 1.3 .. 4 KB, register cap of the 32x32x32 variants
 #ifndef BQQ_MID_STAGES
 #define BQQ_MID_STAGES 3
 #endif
@@ -51,7 +56,7 @@ struct DecodePlan {
   int sgw;         // super-groups per warp
   int bpc;         // bit layers per CTA (kDW warps each): 1, or all of them for short single-chunk layers
   int nchunks;     // chunks per bit layer
-  int nparts;      // partial sums per output = bw * nchunks
+  int nparts;      // partial sums per output = (bw / bpc) * nchunks
   size_t smem;
   size_t partial_floats;
   size_t xdig_bytes, xmeta_bytes;   // workspace regions written by the activation preparation kernel
