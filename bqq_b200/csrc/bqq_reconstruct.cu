@@ -32,9 +32,28 @@ __device__ __forceinline__ uint32_t nibble_to_bytes(uint32_t n) { return (n * 0x
 // Collect the least significant bits of 4 bytes into a nibble (byte e -> bit e).
 __device__ __forceinline__ uint32_t bytes_to_nibble(uint32_t y) { return ((y & 0x01010101u) * 0x01020408u) >> 24; }
 
-template <int RT>
+// element type of W as a compile-time choice: the store loop is the bulk of the kernel
+template <int DT> struct WType;
+template <> struct WType<BQQ_F32> {
+  using T = float;
+  static __device__ __forceinline__ T cvt(float v) { return v; }
+  static __device__ __forceinline__ float back(T v) { return v; }
+};
+template <> struct WType<BQQ_BF16> {
+  using T = __nv_bfloat16;
+  static __device__ __forceinline__ T cvt(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float back(T v) { return __bfloat162float(v); }
+};
+template <> struct WType<BQQ_F16> {
+  using T = __half;
+  static __device__ __forceinline__ T cvt(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float back(T v) { return __half2float(v); }
+};
+
+template <int RT, int DT, bool LO>
 __global__ void __launch_bounds__(kReconWarps * 32)
 bqq_reconstruct_kernel(const ReconParams p) {
+  using WT = typename WType<DT>::T;
   const Geom& g = p.g;
   const int lane = threadIdx.x & 31;
   const float scale = p.bound_parts ? p.scale * w_scale_from_bound(p.bound_parts, (float)(g.bw * g.r)) : p.scale;
@@ -104,16 +123,34 @@ bqq_reconstruct_kernel(const ReconParams p) {
     }
     const int prow_max = min(32, g.P - 32 * pt);
     const int ql = 32 * qt + lane;
+    const size_t at0 = (size_t)(i * g.P + 32 * pt) * ldw + (size_t)j * g.Q + ql;
+    WT* wrow = reinterpret_cast<WT*>(p.W) + at0;
+    WT* lrow = LO ? reinterpret_cast<WT*>(p.W_lo) + at0 : nullptr;
+    const bool col_ok = ql < g.Q;
 #pragma unroll
     for (int pp = 0; pp < 32; ++pp) {
       const float rterm = __shfl_sync(0xffffffffu, rowterm, pp);
-      if (pp < prow_max && ql < g.Q) {
-        const size_t at = (size_t)(i * g.P + 32 * pt + pp) * ldw + (size_t)j * g.Q + ql;
+      if (pp < prow_max && col_ok) {
         const float w = (acc[pp] + colterm + rterm) * scale;
-        store_from_float(p.W, at, p.w_dtype, w);
-        if (p.W_lo) store_from_float(p.W_lo, at, p.w_dtype, w - round_to(w, p.w_dtype));
+        const WT wv = WType<DT>::cvt(w);
+        wrow[(size_t)pp * ldw] = wv;
+        if (LO) lrow[(size_t)pp * ldw] = WType<DT>::cvt(w - WType<DT>::back(wv));
       }
     }
+  }
+}
+
+template <int RT>
+static void reconstruct_dispatch(const ReconParams& p, int blocks, cudaStream_t st) {
+  const int threads = kReconWarps * 32;
+  const bool lo = p.W_lo != nullptr;
+  if (p.w_dtype == BQQ_F32) bqq_reconstruct_kernel<RT, BQQ_F32, false><<<blocks, threads, 0, st>>>(p);
+  else if (p.w_dtype == BQQ_BF16) {
+    if (lo) bqq_reconstruct_kernel<RT, BQQ_BF16, true><<<blocks, threads, 0, st>>>(p);
+    else bqq_reconstruct_kernel<RT, BQQ_BF16, false><<<blocks, threads, 0, st>>>(p);
+  } else {
+    if (lo) bqq_reconstruct_kernel<RT, BQQ_F16, true><<<blocks, threads, 0, st>>>(p);
+    else bqq_reconstruct_kernel<RT, BQQ_F16, false><<<blocks, threads, 0, st>>>(p);
   }
 }
 
@@ -127,8 +164,9 @@ int reconstruct_launch(const BqqLayer* L, void* W, void* W_lo, int w_dtype, floa
   p.total_tasks = (long long)p.g.rw * p.g.cw * p.g.PT * p.g.QT;
   long long blocks = (p.total_tasks + kReconWarps - 1) / kReconWarps;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
-  if (p.g.RT == 1) bqq_reconstruct_kernel<1><<<(int)blocks, kReconWarps * 32, 0, st>>>(p);
-  else bqq_reconstruct_kernel<2><<<(int)blocks, kReconWarps * 32, 0, st>>>(p);
+  if (w_dtype == BQQ_F32 && W_lo) return BQQ_ERR_UNSUPPORTED;     // a second part only exists for 16-bit types
+  if (p.g.RT == 1) reconstruct_dispatch<1>(p, (int)blocks, st);
+  else reconstruct_dispatch<2>(p, (int)blocks, st);
   return launch_status();
 }
 
