@@ -456,6 +456,11 @@ bqq_decode_kernel(const DecodeParams p) {
   // statistics):  alpha = a * scale,  beta = b * sum,  gamma = c * scale;  d * sum is summed right
   // here.  The fixed-point scale of u for this warp comes from the bound |a| sum|x| + |b| |sum x|.
   constexpr float kUOff = 4128768.f;                 // 63 * 65536: the offset touches the top digit only
+  // u is scaled so that the bound maps to kUScale, 0.8 % inside the offset: t is computed from the rounded
+  // x digits and can exceed the bound taken from the unrounded x by up to Q / 65024 of it (and does, for
+  // narrow patches whose Z row is all ones and whose x share one sign); without the slack such a rank fell
+  // below 2^23 and its digits were garbage
+  constexpr float kUScale = 4096000.f;
   // float -> integer by mantissa alignment: 2^23 + kUOff + round(u * inv_us); the low three bytes of
   // the float's bit pattern are then the unsigned base-256 digits of round(u * inv_us) + kUOff
   constexpr float kMagic = 8388608.f + kUOff;
@@ -496,8 +501,9 @@ bqq_decode_kernel(const DecodeParams p) {
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ub = fmaxf(ub, __shfl_xor_sync(0xffffffffu, ub, o));
-  // u * inv_us lies in [-kUOff, kUOff]; adding kUOff makes it a non-negative 23-bit integer
-  const float inv_us = ub > 0.f ? kUOff / ub : 0.f;
+  // u * inv_us lies in [-kUScale, kUScale] (a little beyond at most); adding kUOff makes it a non-negative
+  // 23-bit integer
+  const float inv_us = ub > 0.f ? kUScale / ub : 0.f;
   // second pass over the lane's own entries: alpha *= inv_us, beta = beta * inv_us + magic, so that one
   // fused multiply-add per rank yields the digits of u
   for (int e = lane; e < nw * kGroup; e += 32) {
@@ -686,7 +692,7 @@ bqq_decode_kernel(const DecodeParams p) {
     for (int o = 16; o >= 4; o >>= 1) cterm += __shfl_xor_sync(0xffffffffu, cterm, o);   // lanes with equal t
   }
   cterm += dacc;
-  const float us = ub * (1.f / kUOff);
+  const float us = ub * (1.f / kUScale);
 #pragma unroll
   for (int nt = 0; nt < NT2; ++nt) {
     // which row of X and which digits this lane's two columns carry: (digit 0, digit 1) or

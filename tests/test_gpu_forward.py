@@ -224,3 +224,41 @@ def test_fused_prologue_and_residual(geom, M, dtype):
         assert O.max_rel_err(got.float().cpu().numpy(), oracle(X.float()) + res.float().numpy()) < tol
         # no fusion at all equals the plain forward bit for bit
         assert torch.equal(bq.forward_fused(X.cuda()), bq(X.cuda()))
+
+
+@pytest.mark.parametrize('M', [1, 4])
+@pytest.mark.parametrize('sign', [1.0, -1.0])
+def test_u_at_its_bound(M, sign):
+    """Every rank's u sits exactly on the bound its fixed-point scale is derived from (Z all ones, x of one
+    sign, a and b of one sign), on the upper and on the lower edge: the digits must not wrap.  With narrow
+    patches this happens by chance (a Z row of ones, 8 inputs of one sign)."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, P, Q, r = 2, 3, 9, 32, 8, 48
+    g = torch.Generator().manual_seed(3)
+    Y = torch.rand(bw, rw, cw, P, r, generator=g) > 0.5
+    Z = torch.ones(bw, rw, cw, r, Q, dtype=torch.bool)
+    A = torch.rand(bw, rw, cw, 4, generator=g) * 0.02 + 0.001
+    A[..., :2] *= sign
+    X = torch.rand(M, cw * Q, generator=g) + 0.1
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    with torch.no_grad():
+        y = bq(X.cuda())
+    ref = oracle_forward_t(Y, Z, A, None, X)
+    assert O.max_rel_err(y.cpu().numpy(), ref) < TOL_FP32
+
+
+def test_narrow_patch_regression():
+    """Seeded case found by a random sweep (P=32, Q=8, r=48, 33 col patches): one rank of one patch exceeded
+    the bound by the rounding of the x digits and its u digits wrapped (3.6e-2 error in one row)."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, P, Q, r, M = 2, 5, 33, 32, 8, 48, 8
+    g = torch.Generator().manual_seed(106)
+    Y = torch.rand(bw, rw, cw, P, r, generator=g) > 0.5
+    Z = torch.rand(bw, rw, cw, r, Q, generator=g) > 0.5
+    A = torch.randn(bw, rw, cw, 4, generator=g) * 0.02
+    X = torch.randn(M, cw * Q, generator=g)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    ref = oracle_forward_t(Y, Z, A, None, X)
+    with torch.no_grad():
+        assert O.max_rel_err(bq(X.cuda()).cpu().numpy(), ref) < TOL_FP32
+        assert O.max_rel_err(bq(X[6:7].cuda()).cpu().numpy(), ref[6:7]) < TOL_FP32
