@@ -95,8 +95,8 @@ def _load():
         'bqq_peer_free': (i32, [vp]),
         'bqq_peer_gather': (i32, [C.POINTER(BqqPeerGroup), vp, i32, i32, i64, i64, vp, i64, vp]),
         'bqq_peer_status': (i32, [C.POINTER(BqqPeerGroup), vp]),
-        'bqq_forward_decode_gathered': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, C.POINTER(BqqPeerGroup), vp, i64,
-                                            vp, sz, vp]),
+        'bqq_forward_decode_gathered': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, C.POINTER(BqqFusion),
+                                            C.POINTER(BqqPeerGroup), vp, i64, vp, sz, vp]),
         'bqq_noalloc_scratch_bytes': (sz, []),
         'bqq_forward_decode_noalloc': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp]),
     }

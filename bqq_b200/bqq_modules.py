@@ -191,6 +191,32 @@ class _BqqForwardMixin:
                       'bqq_forward_prefill')
         return y.reshape(*X.shape[:-1], out_f)
 
+    def _fusion(self, M, rms_weight, eps, swiglu, res2d):
+        """BqqFusion descriptor for bqq_forward_decode_fused / _gathered; res2d is [M, out] (any row pitch)."""
+        in_f = self.col_width * self.z_col
+        out_f = self.row_width * self.y_row
+        fusion = _cabi.BqqFusion()
+        keep = []
+        if rms_weight is not None:
+            w = rms_weight.detach()
+            _require_cuda(w, 'the normalisation weight')
+            if w.dtype not in _DTYPE_CODE or w.numel() != in_f:
+                raise RuntimeError('bqq_b200: rms_weight must be an fp32/bf16/fp16 vector of in_features elements')
+            w = w.contiguous()
+            keep.append(w)
+            fusion.prologue, fusion.norm_weight, fusion.norm_dtype, fusion.eps = (
+                _cabi.PRO_RMSNORM, w.data_ptr(), _DTYPE_CODE[w.dtype], float(eps))
+        elif swiglu:
+            fusion.prologue = _cabi.PRO_SWIGLU
+        if res2d is not None:
+            if (not res2d.is_cuda or tuple(res2d.shape) != (M, out_f) or res2d.stride(-1) != 1
+                    or res2d.dtype not in _DTYPE_CODE):
+                raise RuntimeError('bqq_b200: residual must be a CUDA tensor [..., out_features] with unit inner stride')
+            keep.append(res2d)
+            fusion.residual, fusion.ld_residual, fusion.residual_dtype = (
+                res2d.data_ptr(), res2d.stride(0), _DTYPE_CODE[res2d.dtype])
+        return fusion, keep
+
     def forward_fused(self, X, rms_weight=None, eps: float = 1e-5, swiglu: bool = False, residual=None):
         """Forward with the neighbouring element-wise operations of a decoder block folded into the
         kernels (bqq_forward_decode_fused):
@@ -225,26 +251,8 @@ class _BqqForwardMixin:
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         y = torch.empty((M, out_f), dtype=X.dtype, device=device)
-        fusion = _cabi.BqqFusion()
-        keep = []
-        if rms_weight is not None:
-            w = rms_weight.detach()
-            _require_cuda(w, 'the normalisation weight')
-            if w.dtype not in _DTYPE_CODE or w.numel() != in_f:
-                raise RuntimeError('bqq_b200: rms_weight must be an fp32/bf16/fp16 vector of in_features elements')
-            w = w.contiguous()
-            keep.append(w)
-            fusion.prologue, fusion.norm_weight, fusion.norm_dtype, fusion.eps = (
-                _cabi.PRO_RMSNORM, w.data_ptr(), _DTYPE_CODE[w.dtype], float(eps))
-        elif swiglu:
-            fusion.prologue = _cabi.PRO_SWIGLU
-        if residual is not None:
-            r2 = residual.reshape(-1, out_f)
-            if (not residual.is_cuda or r2.shape[0] != M or r2.stride(-1) != 1 or residual.dtype not in _DTYPE_CODE):
-                raise RuntimeError('bqq_b200: residual must be a CUDA tensor [..., out_features] with unit inner stride')
-            keep.append(r2)
-            fusion.residual, fusion.ld_residual, fusion.residual_dtype = (
-                r2.data_ptr(), r2.stride(0), _DTYPE_CODE[residual.dtype])
+        fusion, keep = self._fusion(M, rms_weight, eps, swiglu,
+                                    None if residual is None else residual.reshape(-1, out_f))
         code = _DTYPE_CODE[X.dtype]
         layer = self._layer(st)
         with torch.cuda.device(device):
@@ -255,13 +263,16 @@ class _BqqForwardMixin:
                   'bqq_forward_decode_fused')
         return y.reshape(*X.shape[:-1], out_f)
 
-    def forward_gathered(self, X, peer, out=None):
+    def forward_gathered(self, X, peer, out=None, rms_weight=None, eps: float = 1e-5, swiglu: bool = False,
+                         residual=None):
         """Forward of a row-patch shard with the column gather built in: every rank calls it on its
         shard with the full activation X [..., in] and gets the full output [..., world*out_local]
         (columns in rank order).  `peer` is a bqq_b200.peer.PeerGatherGroup of the ranks.
 
         Up to 16 rows the decode kernel itself stores each finished row patch into the peers' gather
-        regions (bqq_forward_decode_gathered); larger batches run the forward and then the gather kernel."""
+        regions (bqq_forward_decode_gathered); larger batches run the forward and then the gather kernel.
+        rms_weight / swiglu / residual as in forward_fused; `residual` is the full [..., world*out_local]
+        tensor, of which this rank adds its own columns before sending."""
         self._check_inference_only(X)
         if X.dtype not in _DTYPE_CODE:
             raise RuntimeError(f'bqq_b200: unsupported activation dtype {X.dtype} (fp32, bf16, fp16 only)')
@@ -269,19 +280,26 @@ class _BqqForwardMixin:
         device = st.zplanes.device
         in_f = self.col_width * self.z_col
         out_f = self.row_width * self.y_row
-        if X.shape[-1] != in_f:
-            raise RuntimeError(f'bqq_b200: last dim of X is {X.shape[-1]}, layer expects {in_f}')
+        width = 2 * in_f if swiglu else in_f
+        if X.shape[-1] != width:
+            raise RuntimeError(f'bqq_b200: last dim of X is {X.shape[-1]}, expected {width}')
         X = X.to(device)
-        x2 = X.reshape(-1, in_f)
+        x2 = X.reshape(-1, width)
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         M = x2.shape[0]
         esize = X.element_size()
+        res_local = None
+        if residual is not None:
+            res_local = residual.reshape(M, peer.world * out_f)[:, peer.rank * out_f:(peer.rank + 1) * out_f]
         fused = (0 < M <= _cabi.DECODE_MAX_M and (out_f * esize) % 4 == 0
                  and (esize == 4 or self.y_row % 2 == 0)
                  and M * out_f * peer.world * esize <= peer.max_bytes)
         if not fused:
-            return peer.gather(self.forward(X), out=out)
+            y_local = self.forward_fused(X, rms_weight=rms_weight, eps=eps, swiglu=swiglu,
+                                         residual=None if res_local is None else res_local.contiguous())
+            return peer.gather(y_local, out=out)
+        fusion, keep = self._fusion(M, rms_weight, eps, swiglu, res_local)
         if out is None:
             out = torch.empty((M, peer.world * out_f), dtype=X.dtype, device=device)
         o2 = out.reshape(M, peer.world * out_f)
@@ -294,7 +312,8 @@ class _BqqForwardMixin:
             nbytes = lib.bqq_decode_workspace_bytes(st.dims, M)
             ws = _workspace(device, 'decode', nbytes)
             check(lib.bqq_forward_decode_gathered(layer, x2.data_ptr(), code, M, x2.stride(0), y.data_ptr(), code,
-                                                  y.stride(0), peer.descriptor(), o2.data_ptr(), o2.stride(0),
+                                                  y.stride(0), C.byref(fusion), peer.descriptor(), o2.data_ptr(),
+                                                  o2.stride(0),
                                                   ws.data_ptr(), ws.numel(),
                                                   torch.cuda.current_stream(device).cuda_stream),
                   'bqq_forward_decode_gathered')

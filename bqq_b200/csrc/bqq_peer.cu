@@ -207,8 +207,8 @@ int bqq_peer_gather(const BqqPeerGroup* g, const void* y_local, int dtype, int r
 }
 
 int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y_local,
-                                int y_dtype, int64_t ldy, const BqqPeerGroup* g, void* gathered, int64_t ld_gathered,
-                                void* workspace, size_t workspace_bytes, void* stream) {
+                                int y_dtype, int64_t ldy, const BqqFusion* fusion, const BqqPeerGroup* g, void* gathered,
+                                int64_t ld_gathered, void* workspace, size_t workspace_bytes, void* stream) {
   if (!layer || !g || !gathered) return BQQ_ERR_NULL;
   if (g->world < 1 || g->world > BQQ_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return BQQ_ERR_BAD_SHAPE;
   if (M <= 0 || M > BQQ_DECODE_MAX_M) return BQQ_ERR_BAD_SHAPE;
@@ -220,7 +220,8 @@ int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtyp
   if ((size_t)M * geo.out_features() * g->world * es > g->gather_bytes) return BQQ_ERR_WORKSPACE;
   // same argument checks as bqq_forward_decode, then the decode kernel with the peer stores in its
   // epilogue, then the receiving kernel (programmatic dependent: it polls while the decode kernel ends)
-  int rc = bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y_local, y_dtype, ldy, workspace, workspace_bytes, stream, g);
+  int rc = bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y_local, y_dtype, ldy, workspace, workspace_bytes, stream, g,
+                                   fusion);
   if (rc) return rc;
   return peer_gather_launch(g, nullptr, y_dtype, M, geo.out_features(), geo.out_features(), gathered, ld_gathered, stream);
 }

@@ -95,14 +95,12 @@ class DecoderLayer(nn.Module):
             return self.peer.gather(y)
         return gather_columns(y)
 
-    def _proj_gathered(self, proj, x):
-        """Row-patch sharded projection with its outputs gathered on every rank."""
-        if self.world == 1:
-            return proj(x)
+    def _proj_gathered(self, proj, x, residual):
+        """residual + row-patch sharded projection, outputs gathered on every rank."""
         rows = x.numel() // x.shape[-1]
         if rows <= 16 and self._fits(rows, proj.row_width * proj.y_row, x.element_size()):
-            return proj.forward_gathered(x, self.peer)
-        return self._gather(proj(x))
+            return proj.forward_gathered(x, self.peer, residual=residual)    # residual added before the rows are sent
+        return residual + self._gather(proj(x))
 
     def forward(self, x, k_cache, v_cache, pos, rot, mask=None):
         """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim].
@@ -114,12 +112,8 @@ class DecoderLayer(nn.Module):
         B, T, _ = x.shape
         hd = cfg.head_dim
         lh, lkv = self.local_heads, self.local_kv
-        fused = self.world == 1          # normalisation, SwiGLU and residual adds folded into the layers' kernels
-        if fused:
-            qkv = self.qkv_proj.forward_fused(x, rms_weight=self.norm1, eps=1e-5)
-        else:
-            qkv = self.qkv_proj(F.rms_norm(x, (cfg.hidden,), self.norm1, 1e-5))
-        qkv = qkv.view(B, T, lh + 2 * lkv, hd)
+        # normalisation, SwiGLU and residual adds are folded into the layers' kernels (forward_fused)
+        qkv = self.qkv_proj.forward_fused(x, rms_weight=self.norm1, eps=1e-5).view(B, T, lh + 2 * lkv, hd)
         qk = _rope(qkv[:, :, :lh + lkv], rot)                        # rotary embedding on q and k heads at once
         q = qk[:, :, :lh].transpose(1, 2)
         k = qk[:, :, lh:].transpose(1, 2)
@@ -134,17 +128,16 @@ class DecoderLayer(nn.Module):
             v_cache.index_copy_(2, pos, v)
             att = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=mask, enable_gqa=True)
         att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
-        if fused:
+        if self.world == 1:
             x = self.o_proj.forward_fused(att, residual=x)
             gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)
             return self.down_proj.forward_fused(gu, swiglu=True, residual=x)
-        x = x + self._proj_gathered(self.o_proj, att)                                       # gather 2
-        hx = F.rms_norm(x, (cfg.hidden,), self.norm2, 1e-5)
-        gu = self.gate_up_proj(hx)
+        x = self._proj_gathered(self.o_proj, att, x)                                        # gather 2
+        gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)
         n = gu.shape[-1] // 2
         act = F.silu(gu[..., :n]) * gu[..., n:]
         act = self._gather(act)                                                             # gather 3
-        return x + self._proj_gathered(self.down_proj, act)                                 # gather 4
+        return self._proj_gathered(self.down_proj, act, x)                                  # gather 4
 
 
 def _rope(x, rot):

@@ -85,6 +85,13 @@ def _worker(rank, world, port, result_dir):
                 for _ in range(2):
                     got = shard.forward_gathered(Xd, grp)
                     assert torch.equal(got, want), (rank, bw, rw, cw, M)
+                # fused normalisation on the way in and residual on the way out, against the unsharded fused call
+                gen = torch.Generator().manual_seed(77)
+                w = (1 + 0.1 * torch.randn(cw * 32, generator=gen)).to(dtype).to(dev)
+                h = torch.randn(M, rw * 32, generator=gen).to(dtype).to(dev)
+                want = full.forward_fused(Xd, rms_weight=w, residual=h)
+                got = shard.forward_gathered(Xd, grp, rms_weight=w, residual=h)
+                assert torch.equal(got, want), (rank, 'fused', bw, rw, cw, M)
         grp.status()
         grp.close()
         with open(os.path.join(result_dir, f'ok{rank}'), 'w') as f:
