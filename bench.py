@@ -232,13 +232,23 @@ def main():
     peer = None
     if world > 1:
         from bqq_b200.peer import PeerGatherGroup
-        peer = PeerGatherGroup(max(world * o * 2 for (o, i, bw) in cfgs), device)
+        try:
+            peer = PeerGatherGroup(max(world * o * 2 for (o, i, bw) in cfgs), device)
+        except RuntimeError as exc:          # raised on every rank alike: fall back to the process group's all-gather
+            if rank == 0:
+                print(f'bench: {exc}; gathering with NCCL instead', file=sys.stderr)
+
+    def gathered_forward(L, x, out):
+        if peer is not None:
+            return L.forward_gathered(x, peer, out=out)        # decode kernel stores its row patches to the peers
+        dist.all_gather_into_tensor(out.view(world, -1), L(x).view(-1))
+        return out
 
     def step():
         with torch.no_grad():
             for n, (L, x) in enumerate(zip(layers, xs)):
                 if world > 1:
-                    L.forward_gathered(x, peer, out=gathers[n])    # decode kernel stores its row patches to the peers
+                    gathered_forward(L, x, gathers[n])
                 else:
                     L(x)
 
@@ -282,7 +292,7 @@ def main():
             with torch.no_grad():
                 for n, L in enumerate(layers):
                     if world > 1:
-                        y = L.forward_gathered(xh[n].to(device, non_blocking=True), peer, out=gathers[n])
+                        y = gathered_forward(L, xh[n].to(device, non_blocking=True), gathers[n])
                         yh[n].copy_(y[:, :yh[n].shape[1]], non_blocking=True)
                     else:
                         bound[n]()                        # one C call: copy in, kernels, copy out
@@ -334,13 +344,16 @@ def main():
             'config': {'workload': 'decode_sweep_b1', 'layers': len(cfgs), 'P': P, 'Q': Q, 'r': R,
                        'activations': 'bf16', 'batch': 1, 'bytes_per_step_per_gpu': step_bytes,
                        'l2': 'working set per step (208.5 MB of packed planes) exceeds the 126 MB L2',
-                       'parallelism': f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel (bqq_forward_decode_gathered)' if world > 1 else 'single GPU'},
+                       'parallelism': 'single GPU' if world == 1 else (
+                           f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel '
+                           '(bqq_forward_decode_gathered)' if peer is not None else
+                           f'row-patch shards x{world}, NCCL all-gather of outputs (peer gather set-up failed)')},
             'e2e': {'value': e2e_val, 'unit': 'GB/s',
                     'h2d_bytes_per_step': sum(i * 2 for (o, i, bw) in cfgs),
                     'd2h_bytes_per_step': sum(o * 2 for (o, i, bw) in cfgs),
                     'steps': e2e_steps, 'ms_per_step': e2e_ms / e2e_steps},
             # decode kernel (+ activation preparation kernel) per layer, + the gather kernel when sharded
-            'gpu_launches': (launches_per_step + (len(cfgs) if world > 1 else 0)) * args.steps,
+            'gpu_launches': (launches_per_step + (len(cfgs) if peer is not None else 0)) * args.steps,
             'roofline': {'bound': 'hbm', 'achieved': per_gpu, 'peak': peak, 'unit': 'GB/s',
                          'frac': per_gpu / peak, 'traffic': TRAFFIC_RATIO * step_bytes / len(cfgs),
                          'traffic_note': 'dram read+write bytes of one ncu capture (4096x14336, 4 bit layers: '

@@ -36,21 +36,41 @@ class PeerGatherGroup:
         self.device = torch.device(device)
         self.max_bytes = int(max_bytes)
         self._regions = [None] * self.world
+        error = None
         with torch.cuda.device(self.device):
             own = C.c_void_p()
             handle = C.create_string_buffer(_cabi.PEER_HANDLE_BYTES)
-            check(lib.bqq_peer_alloc(self.max_bytes, C.byref(own), handle), 'bqq_peer_alloc')
-            self._regions[self.rank] = own.value
+            rc = lib.bqq_peer_alloc(self.max_bytes, C.byref(own), handle)
+            if rc:
+                error = f'bqq_peer_alloc: {_cabi.strerror(rc)}'
+            else:
+                self._regions[self.rank] = own.value
+            # every rank takes part in both exchanges whatever happened locally, so that a failure on one rank
+            # becomes an exception on all of them instead of a hang
             handles = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
-            for q in range(self.world):
-                if q == self.rank:
-                    continue
-                p = C.c_void_p()
-                check(lib.bqq_peer_open(handles[q], C.byref(p)), f'bqq_peer_open(rank {q})')
-                self._regions[q] = p.value
-            torch.cuda.synchronize(self.device)
-        dist.barrier(group=group)                    # every region is zeroed and mapped everywhere
+            dist.all_gather_object(handles, None if error else handle.raw, group=group)
+            if error is None and any(h is None for h in handles):
+                error = 'a peer could not allocate its region'
+            if error is None:
+                for q in range(self.world):
+                    if q == self.rank:
+                        continue
+                    p = C.c_void_p()
+                    rc = lib.bqq_peer_open(handles[q], C.byref(p))
+                    if rc:
+                        error = f'bqq_peer_open(rank {q}): {_cabi.strerror(rc)} (CUDA IPC between these processes?)'
+                        break
+                    self._regions[q] = p.value
+                torch.cuda.synchronize(self.device)
+            errors = [None] * self.world
+            dist.all_gather_object(errors, error, group=group)     # also the barrier: every region is zeroed and mapped
+            if any(errors):
+                for q, p in enumerate(self._regions):
+                    if p is not None:
+                        (lib.bqq_peer_free if q == self.rank else lib.bqq_peer_close)(p)
+                self._regions = None
+                raise RuntimeError('bqq_b200: peer gather group could not be set up: '
+                                   + '; '.join(f'rank {q}: {e}' for q, e in enumerate(errors) if e))
         self._desc = BqqPeerGroup(self.rank, self.world, (C.c_void_p * _cabi.MAX_PEERS)(*self._regions),
                                   self.max_bytes)
 
