@@ -25,10 +25,15 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   if (pl.variant < 0) { pl.smem = 0; return pl; }
   pl.NB = M <= 1 ? 1 : 4;
   pl.mtiles = (M + pl.NB - 1) / pl.NB;
-  // chunks per (row patch, bit layer): long chunks amortise the per-warp set-up, two chunks keep enough
-  // CTAs in flight on wide layers (measured on 2048..14336 input features)
-  int nchunks = g.JG <= 32 ? 1 : (g.JG <= 128 ? 2 : (g.JG + 63) / 64);
-  if (pl.NB > 1 && g.JG > 64) nchunks = (g.JG + 31) / 32;   // batched rows: shorter chunks balance better
+  // chunks per (row patch, bit layer), from measured sweeps on 2048..14336 input features: one chunk up to
+  // 32 col-patch groups (and then one CTA for all bit layers at M = 1), two up to 64; wider layers want about
+  // 8 CTAs per row patch over all bit layers (4 chunks at 2 bit layers, 2 at 4), chunks of at least 16 groups
+  int nchunks = g.JG <= 32 ? 1 : 2;
+  if (g.JG > 64) {
+    const int k = (g.JG + 127) / 128;
+    nchunks = std::max(k, std::min(g.JG / 16, (8 * k + g.bw / 2) / g.bw));
+  }
+  if (pl.NB > 1 && g.JG > 64) nchunks = std::max(nchunks, (g.JG + 31) / 32);   // batched rows: shorter chunks balance better
   int sgw = (g.JG + kDW * nchunks - 1) / (kDW * nchunks);
   if (sgw > kMaxSgw) sgw = kMaxSgw;
   pl.sgw = sgw;
