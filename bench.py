@@ -39,6 +39,7 @@ SHAPES = [(2048, 2048), (2048, 6144), (6144, 2048), (4096, 14336)]   # (out, in)
 BITS = [2, 3, 4]
 P = Q = R = 32
 L2_BYTES = 126e6
+PEER_TIMEOUT = False   # set when a bounded wait of the peer gather gave up (reported in the JSON line)
 TRAFFIC_RATIO = 62.09 / 61.72   # measured DRAM bytes / algorithmic bytes (profiles/decode_kernel_4096x14336_bw4_m1.md)
 
 
@@ -185,7 +186,12 @@ def shutdown(world, graphs, peer=None):
         timer.daemon = True
         timer.start()
         if peer is not None:
-            peer.status()              # raises if a bounded wait on a peer gave up during the run
+            try:
+                peer.status()          # raises if a bounded wait on a peer gave up during the run
+            except RuntimeError as exc:
+                print(f'bench: {exc}: the gathered outputs of this run are not valid', file=sys.stderr)
+                global PEER_TIMEOUT
+                PEER_TIMEOUT = True
             peer.close()
         dist.barrier()
         dist.destroy_process_group()
@@ -346,7 +352,8 @@ def main():
                        'l2': 'working set per step (208.5 MB of packed planes) exceeds the 126 MB L2',
                        'parallelism': 'single GPU' if world == 1 else (
                            f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel '
-                           '(bqq_forward_decode_gathered)' if peer is not None else
+                           '(bqq_forward_decode_gathered)' + (' -- A PEER WAIT TIMED OUT, RESULT INVALID' if PEER_TIMEOUT else '')
+                           if peer is not None else
                            f'row-patch shards x{world}, NCCL all-gather of outputs (peer gather set-up failed)')},
             'e2e': {'value': e2e_val, 'unit': 'GB/s',
                     'h2d_bytes_per_step': sum(i * 2 for (o, i, bw) in cfgs),
