@@ -37,7 +37,8 @@
 
 namespace bqq {
 
-// tunables (measured on B200): ring slots for slot sizes of 1.3 .. 4 KB, register cap of the 32x32x32 variants
+// tunables (measured on B200): ring slots for slot sizes of 1.3 .. 4 KB, register cap of the 32x32x32 variant
+// with 4 rows of X (the batch-1 variant is capped at 72 registers = 7 CTAs per SM, 80 when one CTA takes all bit layers)
 #ifndef BQQ_MID_STAGES
 #define BQQ_MID_STAGES 3
 #endif
@@ -304,7 +305,7 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
 
 // MB: the CTA takes all bit layers of its row patch (4 warps each) instead of one.
 template <int PT, int QT, int RT, int NB, bool MB>
-__global__ void __maxnreg__(PT == 1 ? (NB == 1 ? 80 : BQQ_NB4_REGS) : 255)
+__global__ void __maxnreg__(PT == 1 ? (NB == 1 ? (MB ? 80 : 72) : BQQ_NB4_REGS) : 255)
 bqq_decode_kernel(const DecodeParams p) {
   const int bpc = MB ? p.bpc : 1;
   constexpr int RP = RT * 32;
