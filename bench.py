@@ -263,10 +263,14 @@ def main():
         for _ in range(3):
             step()
         stream.synchronize()
+        # several steps per captured graph (a decoder model replays hundreds of layers per graph launch; one
+        # step here has 12): the steps run back to back without a host round trip in between
+        group = next(g for g in (10, 5, 4, 2, 1) if args.steps % g == 0)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            step()
-        for _ in range(args.warmup):
+            for _ in range(group):
+                step()
+        for _ in range((args.warmup + group - 1) // group):
             graph.replay()
         stream.synchronize()
         if world > 1:
@@ -277,7 +281,7 @@ def main():
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(args.steps):
+        for _ in range(args.steps // group):
             graph.replay()
         e1.record(stream)
         stream.synchronize()
@@ -349,6 +353,7 @@ def main():
             'data': 'synthetic',
             'config': {'workload': 'decode_sweep_b1', 'layers': len(cfgs), 'P': P, 'Q': Q, 'r': R,
                        'activations': 'bf16', 'batch': 1, 'bytes_per_step_per_gpu': step_bytes,
+                       'steps_per_graph_launch': group,
                        'l2': 'working set per step (208.5 MB of packed planes) exceeds the 126 MB L2',
                        'parallelism': 'single GPU' if world == 1 else (
                            f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel '
