@@ -39,8 +39,11 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   pl.sgw = sgw;
   pl.nchunks = (g.JG + kDW * sgw - 1) / (kDW * sgw);
   // short single-chunk layers at batch 1: one CTA takes all bit layers of a row patch, so the sums never
-  // leave the CTA (no scratch round trip); 4 warps per bit layer, at most 16 warps
-  pl.bpc = (pl.variant == 0 && pl.NB == 1 && pl.nchunks == 1 && g.bw <= 4) ? g.bw : 1;
+  // leave the CTA (no scratch round trip); 4 warps per bit layer, at most 16 warps.  Tall layers (many row
+  // patches) fill the machine better with one CTA per bit layer (measured: 6144x4096 prefers the former,
+  // 28672x4096 the latter).  Both routes add in the same order and give identical bits, so this one choice
+  // may depend on the number of row patches.
+  pl.bpc = (pl.variant == 0 && pl.NB == 1 && pl.nchunks == 1 && g.bw <= 4 && g.rw * g.bw * kDW <= 3072) ? g.bw : 1;
   pl.nparts = (g.bw / pl.bpc) * pl.nchunks;
   const int PTv = kVariantPT[pl.variant], QTv = kVariantQT[pl.variant], RTv = kVariantRT[pl.variant];
   pl.smem = (size_t)DecodeSmem(sgw, pl.NB, PTv, QTv, RTv, pl.bpc).total;

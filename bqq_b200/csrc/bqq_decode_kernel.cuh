@@ -733,14 +733,20 @@ bqq_decode_kernel(const DecodeParams p) {
   // ---- CTA result, then the cross-CTA reduction in a fixed order (warp 0) ---------------------
   const int nparts = nbg * p.nchunks;
   const int part = bitgroup * p.nchunks + chunk;
-  const int nwarps = kDW * bpc;
   const int mrows = p.mtiles * NB;
   const size_t out_stride = (size_t)p.rw * PP;
   if (nparts == 1) {
     for (int idx = lane; idx < NB * PP; idx += 32) {
       const int beta = idx / PP, pp = idx % PP;
       float v = 0.f;
-      for (int w = 0; w < nwarps; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
+      // same association as the scratch route (the 4 warps of a bit layer first, then the bit layers in
+      // order), so that both routes give identical bits
+      for (int b = 0; b < bpc; ++b) {
+        float sb = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDW; ++w) sb += red[(size_t)((b * kDW + w) * NB + beta) * PP + pp];
+        v += sb;
+      }
       const bool valid = pp < p.P && m0 + beta < p.M;
       const int o = i * p.P + pp;
       if (valid) {
@@ -755,7 +761,12 @@ bqq_decode_kernel(const DecodeParams p) {
   for (int idx = lane; idx < NB * PP; idx += 32) {
     const int beta = idx / PP, pp = idx % PP;
     float v = 0.f;
-    for (int w = 0; w < nwarps; ++w) v += red[(size_t)(w * NB + beta) * PP + pp];
+    for (int b = 0; b < bpc; ++b) {
+      float sb = 0.f;
+#pragma unroll
+      for (int w = 0; w < kDW; ++w) sb += red[(size_t)((b * kDW + w) * NB + beta) * PP + pp];
+      v += sb;
+    }
     p.partial[((size_t)part * mrows + m0 + beta) * out_stride + (size_t)i * PP + pp] = v;
   }
   // the lanes' partial sums are ordered before lane 0's fence by the warp barrier, the fence before

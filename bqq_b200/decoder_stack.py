@@ -9,8 +9,9 @@ lm_head kept dense because the reference's replacement skips names containing 'h
 decode loop (lm/benchmark_inference.py:24-85): random binary factors, greedy decode with a
 KV cache.
 
-Only the BinaryQuadratic layers are the product here; normalisation, rotary embedding,
-attention and the dense lm_head are plain torch ops (plumbing).  With world > 1 the layers are
+Only the BinaryQuadratic layers are the product here; rotary embedding, cache append and attention
+are one flash_attn library call where that package is present (plain torch ops otherwise), the dense
+lm_head is a torch matmul (plumbing).  With world > 1 the layers are
 column-parallel (bqq_b200/sharded.py): q/k/v (one stacked layer) are sharded by heads so attention
 runs on local heads, gate/up (one stacked layer) share one sharding so SwiGLU is local, o_proj and down_proj are row-patch
 sharded; four gathers per layer, all without reductions.  With a PeerGatherGroup the gathers are the
@@ -30,6 +31,11 @@ import torch.nn.functional as F
 
 from .bqq_modules import BinaryQuadratic
 from .sharded import gather_columns
+
+try:        # library kernel for the attention part of the harness: rotary embedding, cache append and attention in one launch
+    from flash_attn import flash_attn_with_kvcache as _flash_kvcache
+except Exception:                                   # not installed: the plain torch ops below do the same
+    _flash_kvcache = None
 
 
 @dataclass
@@ -102,32 +108,42 @@ class DecoderLayer(nn.Module):
             return proj.forward_gathered(x, self.peer, residual=residual)    # residual added before the rows are sent
         return residual + self._gather(proj(x))
 
-    def forward(self, x, k_cache, v_cache, pos, rot, mask=None):
-        """x [B, T, hidden]; caches [B, local_kv, max_seq, head_dim].
+    def forward(self, x, k_cache, v_cache, pos, rot, mask=None, fa=None):
+        """x [B, T, hidden]; caches [B, max_seq, local_kv, head_dim].
 
         Prefill: `pos` is a Python int, positions pos..pos+T are written and attention is causal over
         the prefix.  Decode (T = 1, graph-capturable): `pos` is a 1-element device tensor, the cache
-        row is written with index_copy_ and `mask` [1,1,1,max_seq] hides the unwritten tail."""
+        row is written with index_copy_ and `mask` [1,1,1,max_seq] hides the unwritten tail.
+        `fa` = (cos, sin, lens): with flash_attn present, rotary embedding, cache append and attention
+        are one library kernel (lens int32 [B] = tokens already in the cache)."""
         cfg = self.cfg
         B, T, _ = x.shape
         hd = cfg.head_dim
         lh, lkv = self.local_heads, self.local_kv
         # normalisation, SwiGLU and residual adds are folded into the layers' kernels (forward_fused)
         qkv = self.qkv_proj.forward_fused(x, rms_weight=self.norm1, eps=1e-5).view(B, T, lh + 2 * lkv, hd)
-        qk = _rope(qkv[:, :, :lh + lkv], rot)                        # rotary embedding on q and k heads at once
-        q = qk[:, :, :lh].transpose(1, 2)
-        k = qk[:, :, lh:].transpose(1, 2)
-        v = qkv[:, :, lh + lkv:].transpose(1, 2)
-        if mask is None:
-            k_cache[:, :, pos:pos + T] = k
-            v_cache[:, :, pos:pos + T] = v
-            att = F.scaled_dot_product_attention(q, k_cache[:, :, :pos + T], v_cache[:, :, :pos + T],
-                                                 is_causal=(T > 1 and pos == 0), enable_gqa=True)
+        if fa is not None and _flash_kvcache is not None and x.dtype in (torch.bfloat16, torch.float16):
+            cos, sin, lens = fa
+            att = _flash_kvcache(qkv[:, :, :lh], k_cache, v_cache, k=qkv[:, :, lh:lh + lkv], v=qkv[:, :, lh + lkv:],
+                                 rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens, causal=True,
+                                 rotary_interleaved=True)                                 # [B, T, lh, hd]
         else:
-            k_cache.index_copy_(2, pos, k)
-            v_cache.index_copy_(2, pos, v)
-            att = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=mask, enable_gqa=True)
-        att = self._gather(att.transpose(1, 2).reshape(B, T, self.local_heads * hd))     # gather 1
+            qk = _rope(qkv[:, :, :lh + lkv], rot)                    # rotary embedding on q and k heads at once
+            q = qk[:, :, :lh].transpose(1, 2)
+            k, v = qk[:, :, lh:], qkv[:, :, lh + lkv:]
+            if mask is None:
+                k_cache[:, pos:pos + T] = k
+                v_cache[:, pos:pos + T] = v
+                att = F.scaled_dot_product_attention(q, k_cache[:, :pos + T].transpose(1, 2),
+                                                     v_cache[:, :pos + T].transpose(1, 2),
+                                                     is_causal=(T > 1 and pos == 0), enable_gqa=True)
+            else:
+                k_cache.index_copy_(1, pos, k)
+                v_cache.index_copy_(1, pos, v)
+                att = F.scaled_dot_product_attention(q, k_cache.transpose(1, 2), v_cache.transpose(1, 2),
+                                                     attn_mask=mask, enable_gqa=True)
+            att = att.transpose(1, 2)
+        att = self._gather(att.reshape(B, T, self.local_heads * hd))                      # gather 1
         if self.world == 1:
             x = self.o_proj.forward_fused(att, residual=x)
             gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)
@@ -161,6 +177,8 @@ class DecoderStack(nn.Module):
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float() / cfg.head_dim))
         ang = torch.arange(cfg.max_seq, device=device).float()[:, None] * inv[None, :]
         self.rot = torch.polar(torch.ones_like(ang), ang)           # e^{i * position * frequency}, [max_seq, head_dim/2]
+        self.cos, self.sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        self.use_flash = _flash_kvcache is not None
 
     def bqq_bytes_per_token(self) -> int:
         """Packed bits + fp32 coefficients streamed per decoded token on this rank."""
@@ -175,7 +193,7 @@ class DecoderStack(nn.Module):
     def new_cache(self, batch: int):
         cfg = self.cfg
         kv = max(1, cfg.kv_heads // self.world)
-        shape = (cfg.layers, 2, batch, kv, cfg.max_seq, cfg.head_dim)
+        shape = (cfg.layers, 2, batch, cfg.max_seq, kv, cfg.head_dim)
         return torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
 
     def _head(self, x_last):
@@ -195,8 +213,9 @@ class DecoderStack(nn.Module):
         x = self.embed[ids]
         T = ids.shape[1]
         rot = self.rot[:T]
+        fa = (self.cos, self.sin, torch.zeros(ids.shape[0], dtype=torch.int32, device=self.device)) if self.use_flash else None
         for li, layer in enumerate(self.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], 0, rot)
+            x = layer(x, cache[li, 0], cache[li, 1], 0, rot, fa=fa)
         return self._head(x[:, -1])
 
     @torch.no_grad()
@@ -206,6 +225,7 @@ class DecoderStack(nn.Module):
         x = self.embed[ids].unsqueeze(1)
         rot = self.rot.index_select(0, pos)
         mask = (torch.arange(self.cfg.max_seq, device=self.device) <= pos).view(1, 1, 1, -1)
+        fa = (self.cos, self.sin, pos.to(torch.int32).expand(ids.shape[0]).contiguous()) if self.use_flash else None
         for li, layer in enumerate(self.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], pos, rot, mask)
+            x = layer(x, cache[li, 0], cache[li, 1], pos, rot, mask, fa=fa)
         return self._head(x[:, -1])

@@ -116,6 +116,16 @@ def test_sharded_rows_equal_unsharded():
     for world in (2, 4, 8):
         parts = [_fwd(shard_rows(bq, r, world), X.cuda()) for r in range(world)]
         assert torch.equal(torch.cat(parts, dim=-1), full)
+    # a tall layer takes one CTA per bit layer, its shards one CTA for all bit layers: still identical bits
+    from bqq_b200 import _cabi
+    Y, Z, A, bias, X = synth_layer(2, 512, 4, 32, 32, 32, 1, seed=9, bias=False)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    assert _cabi.lib.bqq_decode_launches(bq._dims(), 1) == 2
+    assert _cabi.lib.bqq_decode_launches(shard_rows(bq, 0, 2)._dims(), 1) == 1
+    full = _fwd(bq, X.cuda())
+    for world in (2, 4):
+        parts = [_fwd(shard_rows(bq, r, world), X.cuda()) for r in range(world)]
+        assert torch.equal(torch.cat(parts, dim=-1), full)
 
 
 @pytest.mark.parametrize('M,dtype', [(1, torch.bfloat16), (3, torch.float32), (40, torch.float16)])
@@ -149,6 +159,7 @@ def test_decode_launch_count():
     assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 32, 32, 32), 4) == 2
     assert lib.bqq_decode_launches(_cabi.dims(2, 128, 448, 32, 32, 32), 1) == 2
     assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 64, 64, 32), 1) == 2
+    assert lib.bqq_decode_launches(_cabi.dims(2, 896, 128, 32, 32, 32), 1) == 2      # tall: one CTA per bit layer
     assert lib.bqq_decode_launches(_cabi.dims(2, 64, 64, 32, 32, 32), 17) < 0
 
 

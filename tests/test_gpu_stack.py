@@ -18,10 +18,10 @@ def _dense_layer(layer, x, k_cache, v_cache, pos, rot, cfg):
     hx = F.rms_norm(xf, (cfg.hidden,), layer.norm1.float(), 1e-5)
     qkv = (hx @ W['qkv_proj'].T).view(B, T, lh + 2 * lkv, hd)
     qk = _rope(qkv[:, :, :lh + lkv], rot)
-    q, k, v = qk[:, :, :lh].transpose(1, 2), qk[:, :, lh:].transpose(1, 2), qkv[:, :, lh + lkv:].transpose(1, 2)
-    k_cache[:, :, pos:pos + T] = k
-    v_cache[:, :, pos:pos + T] = v
-    att = F.scaled_dot_product_attention(q, k_cache[:, :, :pos + T], v_cache[:, :, :pos + T],
+    q = qk[:, :, :lh].transpose(1, 2)
+    k_cache[:, pos:pos + T] = qk[:, :, lh:]
+    v_cache[:, pos:pos + T] = qkv[:, :, lh + lkv:]
+    att = F.scaled_dot_product_attention(q, k_cache[:, :pos + T].transpose(1, 2), v_cache[:, :pos + T].transpose(1, 2),
                                          is_causal=(T > 1 and pos == 0), enable_gqa=True)
     att = att.transpose(1, 2).reshape(B, T, lh * hd)
     xf = xf + att @ W['o_proj'].T
@@ -51,8 +51,9 @@ def test_tiny_stack_matches_dense_recomputation_and_graph_replay():
         xd = x.float()
         dcache = torch.zeros_like(cache, dtype=torch.float32)
         rot = model.rot[:9]
+        fa = (model.cos, model.sin, torch.zeros(2, dtype=torch.int32, device=dev)) if model.use_flash else None
         for li, layer in enumerate(model.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], 0, rot)
+            x = layer(x, cache[li, 0], cache[li, 1], 0, rot, fa=fa)
             xd = _dense_layer(layer, xd, dcache[li, 0], dcache[li, 1], 0, rot, cfg)
         err = (x.float() - xd).abs().max() / xd.abs().max()
         assert err < 3e-2, err                      # bf16 hidden states through two blocks
@@ -61,8 +62,9 @@ def test_tiny_stack_matches_dense_recomputation_and_graph_replay():
         x = model.embed[prompt[:, :1]]
         xd = x.float()
         rot1 = model.rot[9:10]
+        fa = (model.cos, model.sin, torch.full((2,), 9, dtype=torch.int32, device=dev)) if model.use_flash else None
         for li, layer in enumerate(model.layers):
-            x = layer(x, cache[li, 0], cache[li, 1], 9, rot1)
+            x = layer(x, cache[li, 0], cache[li, 1], 9, rot1, fa=fa)
             xd = _dense_layer(layer, xd, dcache[li, 0], dcache[li, 1], 9, rot1, cfg)
         err = (x.float() - xd).abs().max() / xd.abs().max()
         assert err < 3e-2, err
