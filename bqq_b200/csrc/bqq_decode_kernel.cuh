@@ -449,8 +449,11 @@ bqq_decode_kernel(const DecodeParams p) {
   constexpr int kURow = 4 * RP + (NB == 1 ? 0 : 16);
   constexpr int kUSub = NB * kURow;                  // bytes of one col patch's u digits
   uint8_t* my_udig = sm + L.udig + (size_t)warp * kGroup * kUSub;
-  for (int e = lane; e < kGroup * kUSub / 4; e += 32)
-    reinterpret_cast<uint32_t*>(my_udig)[e] = (((4 * e) % kUSub) % kURow) / RP == 3 ? 0x01010101u : 0u;
+  // only the ones need writing: slots 0..2 are fully rewritten before every use
+  for (int e = lane; e < kGroup * NB * (RP / 4); e += 32) {
+    const int sub = e / (NB * (RP / 4)), rem = e % (NB * (RP / 4));
+    reinterpret_cast<uint32_t*>(my_udig + sub * kUSub + (rem / (RP / 4)) * kURow + 3 * RP)[rem % (RP / 4)] = 0x01010101u;
+  }
   bool ok = mbar_wait(bar, 0);
 
   // ---- fold the x statistics into the coefficients of this warp's patch-bits (in place of the
