@@ -8,7 +8,7 @@ import sys
 
 from . import _cabi  # noqa: F401  (fails loudly when the CUDA library is missing)
 from . import bqq_modules
-from .bqq_modules import (BinaryQuadratic, PackedBinaryQuadratic, get_matrices,  # noqa: F401
+from .bqq_modules import (BinaryQuadratic, PackedBinaryQuadratic, PlaneBinaryQuadratic, get_matrices,  # noqa: F401
                           pack_binaryquadratic_model, replace_linear_with_bqq, shard_rows)
 
 
