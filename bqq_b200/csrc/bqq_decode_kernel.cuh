@@ -772,15 +772,13 @@ bqq_decode_kernel(const DecodeParams p) {
     }
     p.partial[((size_t)part * mrows + m0 + beta) * out_stride + (size_t)i * PP + pp] = v;
   }
-  // the lanes' partial sums are ordered before lane 0's fence by the warp barrier, the fence before
-  // the ticket; the CTA that draws the last ticket sees every other CTA's partial sums
+  // the lanes' partial sums are ordered before lane 0's ticket by the warp barrier, and the ticket is one
+  // acquire-release atomic at GPU scope: the CTA that draws the last ticket sees every other CTA's sums
   __syncwarp();
   unsigned ticket = 0;
-  if (lane == 0) {
-    __threadfence();
-    ticket = atomicAdd(p.counters + i * p.mtiles + blockIdx.y, 1u);
-    __threadfence();
-  }
+  if (lane == 0)
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                 : "=r"(ticket) : "l"(p.counters + i * p.mtiles + blockIdx.y) : "memory");
   ticket = __shfl_sync(0xffffffffu, ticket, 0);
   if (ticket != (unsigned)(nparts - 1)) return;
   for (int idx = lane; idx < NB * PP; idx += 32) {
