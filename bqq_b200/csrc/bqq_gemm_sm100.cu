@@ -261,25 +261,81 @@ __global__ void stage_x_kernel(const void* __restrict__ x, int x_dtype, int64_t 
 
 // bf16 rows -> fp16 rows scaled by a per-row power of two (max |x| of the row maps to at most 2^14,
 // so nothing overflows and every bf16 value in range converts exactly); row_unscale[m] = 1 / scale.
-// One warp per row.
-__global__ void stage_x_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int M, int K,
-                                           __half* __restrict__ out, float* __restrict__ row_unscale) {
-  const int lane = threadIdx.x & 31;
-  const int m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (m >= M) return;
-  const __nv_bfloat16* row = x + (size_t)m * ldx;
-  float amax = 0.f;
-  for (int k = lane; k < K; k += 32) amax = fmaxf(amax, fabsf(__bfloat162float(row[k])));
+// One block per row; with `vec` a thread moves 8 values per access and keeps its first kStageKeep
+// accesses in registers, so rows up to 8 * kStageKeep * blockDim.x values are read once.
+constexpr int kStageThreads = 256;
+constexpr int kStageKeep = 2;
+__global__ void __launch_bounds__(kStageThreads)
+stage_x_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int M, int K,
+                           __half* __restrict__ out, float* __restrict__ row_unscale, int vec) {
+  __shared__ float warp_max[kStageThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31;
+  for (int m = blockIdx.x; m < M; m += gridDim.x) {
+    const __nv_bfloat16* row = x + (size_t)m * ldx;
+    const uint4* row8 = reinterpret_cast<const uint4*>(row);
+    const int K8 = K >> 3;
+    uint4 keep[kStageKeep];
+    float amax = 0.f;
+    if (vec) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  float scale = 1.f;
-  if (amax > 0.f && isfinite(amax)) {
-    int e;
-    frexpf(amax, &e);                        // amax = f * 2^e, f in [0.5, 1)
-    scale = exp2f((float)max(-100, min(100, 14 - e)));
+      for (int s = 0; s < kStageKeep; ++s) {
+        const int k = tid + s * kStageThreads;
+        keep[s] = k < K8 ? row8[k] : make_uint4(0u, 0u, 0u, 0u);
+      }
+      for (int k = tid + kStageKeep * kStageThreads; k < K8; k += kStageThreads) {
+        const uint4 v = row8[k];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[e] << 16)), fabsf(__uint_as_float(w[e] & 0xFFFF0000u))));
+      }
+#pragma unroll
+      for (int s = 0; s < kStageKeep; ++s) {
+        const uint32_t w[4] = {keep[s].x, keep[s].y, keep[s].z, keep[s].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w[e] << 16)), fabsf(__uint_as_float(w[e] & 0xFFFF0000u))));
+      }
+    } else {
+      for (int k = tid; k < K; k += kStageThreads) amax = fmaxf(amax, fabsf(__bfloat162float(row[k])));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    __syncthreads();                               // the previous row's readers are done with warp_max
+    if (lane == 0) warp_max[tid >> 5] = amax;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kStageThreads / 32; ++w) amax = fmaxf(amax, warp_max[w]);
+    float scale = 1.f;
+    if (amax > 0.f && isfinite(amax)) {
+      int e;
+      frexpf(amax, &e);                        // amax = f * 2^e, f in [0.5, 1)
+      scale = exp2f((float)max(-100, min(100, 14 - e)));
+    }
+    if (vec) {
+      uint4* out8 = reinterpret_cast<uint4*>(out + (size_t)m * K);
+      auto convert = [scale](const uint4& v) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t h[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __half2 t = __floats2half2_rn(__uint_as_float(w[e] << 16) * scale,
+                                              __uint_as_float(w[e] & 0xFFFF0000u) * scale);
+          h[e] = *reinterpret_cast<const uint32_t*>(&t);
+        }
+        return make_uint4(h[0], h[1], h[2], h[3]);
+      };
+#pragma unroll
+      for (int s = 0; s < kStageKeep; ++s) {
+        const int k = tid + s * kStageThreads;
+        if (k < K8) out8[k] = convert(keep[s]);
+      }
+      for (int k = tid + kStageKeep * kStageThreads; k < K8; k += kStageThreads) out8[k] = convert(row8[k]);
+    } else {
+      for (int k = tid; k < K; k += kStageThreads) out[(size_t)m * K + k] = __float2half_rn(__bfloat162float(row[k]) * scale);
+    }
+    if (tid == 0) row_unscale[m] = 1.f / scale;
   }
-  for (int k = lane; k < K; k += 32) out[(size_t)m * K + k] = __float2half_rn(__bfloat162float(row[k]) * scale);
-  if (lane == 0) row_unscale[m] = 1.f / scale;
 }
 
 // ---- host side -----------------------------------------------------------------
@@ -376,8 +432,9 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   const float* row_unscale = nullptr;
   if (x_dtype == BQQ_BF16) {
     float* unscale = reinterpret_cast<float*>(xlo);          // the lo region is free on this path
-    stage_x_bf16_to_f16_kernel<<<(M + 7) / 8, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx, M, K,
-                                                           reinterpret_cast<__half*>(xhi), unscale);
+    const int vec = (K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
+    stage_x_bf16_to_f16_kernel<<<M, kStageThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx, M, K,
+                                                           reinterpret_cast<__half*>(xhi), unscale, vec);
     rc = launch_status();
     if (rc) return rc;
     a_ptr = xhi;

@@ -1,13 +1,16 @@
 // Dense weight from packed planes:
 //   W[i*P+p, j*Q+q] = sum_b ( a_b popc(Yrow_b[p] & Zcol_b[q]) + b_b popc(Yrow_b[p])
 //                             + c_b popc(Zcol_b[q]) ) + d
-// i.e. BinaryQuadratic.get_weight (neural_network_compression/src/bqq_modules.py:48-55),
-// with the AND+popcount idea of reconstruct_W_kernel (src/bqq_cuda.cu:198-246).
-// A warp owns one 32x32 block of one patch: lane l first gathers row l of Y and
-// column l of Z (bits over the rank) out of the fragment-ordered plane words with
-// nibble/byte multiply tricks, then the block is produced row by row (row words
-// broadcast by shuffle, accumulators in registers) so every store is a contiguous
-// 32-element run.
+// i.e. BinaryQuadratic.get_weight (neural_network_compression/src/bqq_modules.py:48-55); replaces
+// reconstruct_W_kernel (src/bqq_cuda.cu:198-246).
+// A warp owns one 32x32 block of one patch and forms the counts Y Z on the tensor cores
+// (mma.sync m16n8k16, fp16 operands that are 2.0 or zero, fp32 accumulators: the sums are exact).  The Y plane word of a lane is already an A fragment (rows of Y over the rank);
+// the Z plane word is a fragment over q, so it is first turned into a B fragment over the rank: a 4x4
+// byte transposition between four lanes and a one-bit exchange between two, three shuffles in all.
+// Row and column sums come from two more products with an all-ones operand, so one bit layer costs
+// 28 MMAs, 44 FMAs and about 80 integer instructions per warp.
+#include <algorithm>
+
 #include "bqq_common.cuh"
 
 namespace bqq {
@@ -23,125 +26,293 @@ struct ReconParams {
   const float* bound_parts;    // optional: entries are also scaled by w_scale_from_bound
   float scale;
   int coef_dtype, w_dtype;
+  int pairs;                   // 1: two neighbouring entries of a row may be stored as one aligned word
   Geom g;
-  long long total_tasks;       // rw * cw * PT * QT
+  int tasks_per_row;           // cw * PT * QT: 32x32 blocks of one row patch
 };
 
-// Spread the 4 low bits of n to the least significant bits of 4 bytes.
-__device__ __forceinline__ uint32_t nibble_to_bytes(uint32_t n) { return (n * 0x00204081u) & 0x01010101u; }
-// Collect the least significant bits of 4 bytes into a nibble (byte e -> bit e).
-__device__ __forceinline__ uint32_t bytes_to_nibble(uint32_t y) { return ((y & 0x01010101u) * 0x01020408u) >> 24; }
-
-// element type of W as a compile-time choice: the store loop is the bulk of the kernel
+// element type of W as a compile-time choice
 template <int DT> struct WType;
 template <> struct WType<BQQ_F32> {
   using T = float;
+  using T2 = float2;
   static __device__ __forceinline__ T cvt(float v) { return v; }
+  static __device__ __forceinline__ T2 cvt2(float v0, float v1) { return make_float2(v0, v1); }
   static __device__ __forceinline__ float back(T v) { return v; }
 };
 template <> struct WType<BQQ_BF16> {
   using T = __nv_bfloat16;
+  using T2 = __nv_bfloat162;
   static __device__ __forceinline__ T cvt(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ T2 cvt2(float v0, float v1) { return __floats2bfloat162_rn(v0, v1); }
   static __device__ __forceinline__ float back(T v) { return __bfloat162float(v); }
 };
 template <> struct WType<BQQ_F16> {
   using T = __half;
+  using T2 = __half2;
   static __device__ __forceinline__ T cvt(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ T2 cvt2(float v0, float v1) { return __floats2half2_rn(v0, v1); }
   static __device__ __forceinline__ float back(T v) { return __half2float(v); }
 };
 
+// Bits POS + 8 ODD and POS + 8 ODD + 16 of w as two fp16 numbers, each 2.0 (0x4000) or zero: entries ODD and
+// ODD + 2 of the four consecutive ranks a plane word holds for one row (column) at in-byte position POS.
+template <int POS, int ODD>
+__device__ __forceinline__ uint32_t bits_as_half2(uint32_t w) {
+  constexpr int src = POS + 8 * ODD;
+  return (src <= 14 ? w << (14 - src) : w >> (src - 14)) & 0x40004000u;
+}
+constexpr uint32_t kOnesHalf2 = 0x3C003C00u;     // 1.0 twice
+constexpr float kBitValue = 2.0f;                // value of a set entry
+
+// D = A B (+ D): A 16x16 (rows g and g+8 of a lane), B 16x8 (column g), fp16 operands, fp32 accumulators.
+// The order of the 16 entries of k is the same in A and B, so any order serves.
+__device__ __forceinline__ void mma_f16_first(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};\n"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Fragments of rank half KH: rows g + 8 R0 and g + 8 (R0 + 1) of Y, entries {0, 2} and {1, 3} of the lane's ranks
+template <int KH, int R0>
+__device__ __forceinline__ void y_frag(uint32_t (&a)[4], uint32_t yw) {
+  a[0] = bits_as_half2<4 * KH + R0, 0>(yw);
+  a[1] = bits_as_half2<4 * KH + R0 + 1, 0>(yw);
+  a[2] = bits_as_half2<4 * KH + R0, 1>(yw);
+  a[3] = bits_as_half2<4 * KH + R0 + 1, 1>(yw);
+}
+// 8-column tile NT of the exchanged Z word, rank half KH
+template <int KH, int NT>
+__device__ __forceinline__ void z_frag(uint32_t (&b)[2], uint32_t zw) {
+  constexpr int pos = 4 * (NT >> 1) + 2 * KH + (NT & 1);
+  b[0] = bits_as_half2<pos, 0>(zw);
+  b[1] = bits_as_half2<pos, 1>(zw);
+}
+
+// First word of Y and of Z (for the lane that reads plane lane `zsrc`) and first coefficient of one 32x32 block.
+struct ReconTask {
+  const uint32_t* y;
+  const uint32_t* z;
+  size_t ci;                   // i * cw + j
+  int i, j, pt, qt;
+};
+
+template <int RT>
+__device__ __forceinline__ ReconTask recon_locate(const ReconParams& p, int i, unsigned tj, int lane, int zsrc) {
+  const Geom& g = p.g;
+  ReconTask t;
+  t.i = i;
+  t.qt = 0; t.pt = 0; t.j = (int)tj;
+  if (g.PT * g.QT != 1) {
+    unsigned u = tj;
+    t.qt = (int)(u % (unsigned)g.QT); u /= (unsigned)g.QT;
+    t.pt = (int)(u % (unsigned)g.PT);
+    t.j = (int)(u / (unsigned)g.PT);
+  }
+  const int sub = t.j % kGroup;
+  const size_t sg0 = (size_t)i * g.NS + t.j / kGroup;
+  t.y = p.yp + ((sg0 * g.PT + t.pt) * RT * 32 + lane) * kGroup + sub;
+  t.z = p.zp + ((sg0 * RT * g.QT + t.qt) * 32 + zsrc) * kGroup + sub;
+  t.ci = (size_t)i * g.cw + t.j;
+  return t;
+}
+
 template <int RT, int DT, bool LO>
-__global__ void __launch_bounds__(kReconWarps * 32)
+__global__ void __launch_bounds__(kReconWarps * 32, 4)
 bqq_reconstruct_kernel(const ReconParams p) {
   using WT = typename WType<DT>::T;
+  using WT2 = typename WType<DT>::T2;
   const Geom& g = p.g;
   const int lane = threadIdx.x & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
   const float scale = p.bound_parts ? p.scale * w_scale_from_bound(p.bound_parts, (float)(g.bw * g.r)) : p.scale;
+  const float s_core = scale / (kBitValue * kBitValue), s_sum = scale / kBitValue;
   const size_t ldw = (size_t)g.cw * g.Q;
-  // this lane as a row of Y (p = 32pt + lane = 32pt + gp + 8rp) and as a column of Z
-  // (q = 32qt + lane = 32qt + 16qh + 4tq + eq)
-  const int gp = lane & 7, rp = lane >> 3;
-  const int qh = (lane >> 4) & 1, tq = (lane >> 2) & 3, eq = lane & 3;
-  const int zbase = 8 * eq + 4 * qh;
+  // Z word -> B fragment.  Name the bits of this lane b4..b0.  It reads the plane word of lane (b0 b3 b2 b1 b4),
+  // whose bit 8e + 4qh + rr is Z[k = 4 b0 + 2 b3 + b2 + 8 rr][q = 16 qh + 8 b1 + 4 b4 + e].  Exchanging the byte
+  // index e with (b3 b2) and bit 0 of rr with b1 leaves byte e' = Z[k = 16 rr1 + 8 b1 + 4 b0 + e'][q = 16 qh +
+  // 8 x + 4 b4 + 2 b3 + b2] at bit 4 qh + 2 rr1 + x of the byte: the B operand of column n = lane / 4 of the
+  // 8-column tile nt = 2 qh + x (q = 8 nt + n), rank half rr1, with the rank order of the Y fragment.
+  const int zsrc = (lane & 0x0E) | ((lane & 1) << 4) | (lane >> 4);
+  const uint32_t sel_a = (lane & 4) ? 0x3715u : 0x6240u;
+  const uint32_t sel_b = (lane & 8) ? 0x3276u : 0x5410u;
+  const uint32_t keep = (lane & 2) ? 0xAAAAAAAAu : 0x55555555u;
+  const int rot = (lane & 2) ? 31 : 1;
+  const size_t ystep = (size_t)g.JG * g.PT * RT * 32 * kGroup, zstep = (size_t)g.JG * RT * g.QT * 32 * kGroup;
+  const size_t cstep = (size_t)g.rw * g.cw;
 
-  for (long long task = (long long)blockIdx.x * kReconWarps + (threadIdx.x >> 5); task < p.total_tasks;
-       task += (long long)gridDim.x * kReconWarps) {
-    long long u = task;
-    const int qt = (int)(u % g.QT); u /= g.QT;
-    const int pt = (int)(u % g.PT); u /= g.PT;
-    const int j = (int)(u % g.cw);
-    const int i = (int)(u / g.cw);
-    const int sub = j % kGroup;
+  // A warp walks blocks first, first + stride, ... of the layer (row patch i, block tj of the row patch); the
+  // plane words and coefficients of the next step, and at the end those of the next block, are fetched one step ahead.
+  const unsigned tpr = (unsigned)p.tasks_per_row;
+  const unsigned stride = gridDim.x * kReconWarps;
+  unsigned tj = blockIdx.x * kReconWarps + (threadIdx.x >> 5);
+  int i = (int)(tj / tpr);
+  tj -= (unsigned)i * tpr;
+  bool have = i < g.rw;
+  ReconTask cur = recon_locate<RT>(p, have ? i : 0, have ? tj : 0u, lane, zsrc);
+  uint32_t yw_n = 0u, zw_n = 0u;
+  float ca_n = 0.f, cb_n = 0.f, cc_n = 0.f, d_n = 0.f;
+  if (have) {
+    yw_n = cur.y[0];
+    zw_n = cur.z[0];
+    ca_n = load_as_float(p.a, cur.ci, p.coef_dtype);
+    cb_n = load_as_float(p.b, cur.ci, p.coef_dtype);
+    cc_n = load_as_float(p.c, cur.ci, p.coef_dtype);
+    d_n = load_as_float(p.d, cur.ci, p.coef_dtype);
+  }
 
-    float acc[32];
+  while (have) {
+    unsigned ntj = tj + stride;
+    int ni = i;
+    if (ntj >= tpr) {
+      const unsigned k = ntj / tpr;
+      ni += (int)k;
+      ntj -= k * tpr;
+    }
+    const bool have_next = ni < g.rw;
+    const ReconTask nxt = have_next ? recon_locate<RT>(p, ni, ntj, lane, zsrc) : cur;
+
+    float acc[2][4][4];          // [16-row tile][8-column tile][fragment entry]
+    float rowt[2][2];            // sum_b b_b popc(Yrow_b) of rows g8 (+8) of each 16-row tile
+    float colt[4][2];            // d + sum_b c_b popc(Zcol_b) of columns 2 t4 (+1) of each 8-column tile
+    const float dterm = d_n * scale;
 #pragma unroll
-    for (int pp = 0; pp < 32; ++pp) acc[pp] = 0.f;
-    float colterm = load_as_float(p.d, (size_t)i * g.cw + j, p.coef_dtype);   // d + sum_b c_b popc(Zcol_b)
-    float rowterm = 0.f;                                                      // sum_b b_b popc(Yrow_b), lane = row
+    for (int mt = 0; mt < 2; ++mt) {
+      rowt[mt][0] = rowt[mt][1] = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) colt[nt][0] = colt[nt][1] = dterm;
+
     for (int b = 0; b < g.bw; ++b) {
-      const size_t ci = ((size_t)b * g.rw + i) * g.cw + j;
-      const float ca = load_as_float(p.a, ci, p.coef_dtype);
-      const float cb = load_as_float(p.b, ci, p.coef_dtype);
-      const float cc = load_as_float(p.c, ci, p.coef_dtype);
-      const size_t sg = (size_t)i * g.NS + (size_t)b * g.JG + j / kGroup;
-      uint32_t yr[RT], zc[RT];
-      int ys = 0, zs = 0;
+      const float ca = ca_n * s_core, cb = cb_n * s_sum, cc = cc_n * s_sum;
+      const bool more = b + 1 < g.bw;
+      if (more || have_next) {
+        const size_t ci = more ? cur.ci + (size_t)(b + 1) * cstep : nxt.ci;
+        ca_n = load_as_float(p.a, ci, p.coef_dtype);
+        cb_n = load_as_float(p.b, ci, p.coef_dtype);
+        cc_n = load_as_float(p.c, ci, p.coef_dtype);
+        if (!more) d_n = load_as_float(p.d, ci, p.coef_dtype);
+      }
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt) {
-        yr[rt] = 0u;
-        zc[rt] = 0u;
-        if (rt < g.RT) {
-          // row of Y: ranks 16kh + 4t + e sit in the words of lanes 4*gp + t at bits 8e + 4kh + rp
-          const uint32_t* yb = p.yp + (((sg * g.PT + pt) * g.RT + rt) * 32) * kGroup + sub;
+        const uint32_t yw = yw_n;
+        uint32_t zw = zw_n;
+        if (rt + 1 < RT) {
+          yw_n = cur.y[(size_t)b * ystep + (size_t)(rt + 1) * 32 * kGroup];
+          zw_n = cur.z[(size_t)b * zstep + (size_t)(rt + 1) * g.QT * 32 * kGroup];
+        } else if (more) {
+          yw_n = cur.y[(size_t)(b + 1) * ystep];
+          zw_n = cur.z[(size_t)(b + 1) * zstep];
+        } else if (have_next) {
+          yw_n = nxt.y[0];
+          zw_n = nxt.z[0];
+        }
+        uint32_t o = __shfl_xor_sync(0xffffffffu, zw, 4);
+        zw = __byte_perm(zw, o, sel_a);
+        o = __shfl_xor_sync(0xffffffffu, zw, 8);
+        zw = __byte_perm(zw, o, sel_b);
+        o = __shfl_xor_sync(0xffffffffu, zw, 2);
+        o = __funnelshift_l(o, o, rot);
+        zw = (zw & keep) | (o & ~keep);
+        // fragments of both rank halves: 16-row tile mt holds rows g8 + 8 (2 mt + h), 8-column tile nt columns 8 nt + n
+        uint32_t a[2][2][4], bz[4][2][2];
+        y_frag<0, 0>(a[0][0], yw); y_frag<1, 0>(a[0][1], yw);
+        y_frag<0, 2>(a[1][0], yw); y_frag<1, 2>(a[1][1], yw);
+        z_frag<0, 0>(bz[0][0], zw); z_frag<1, 0>(bz[0][1], zw);
+        z_frag<0, 1>(bz[1][0], zw); z_frag<1, 1>(bz[1][1], zw);
+        z_frag<0, 2>(bz[2][0], zw); z_frag<1, 2>(bz[2][1], zw);
+        z_frag<0, 3>(bz[3][0], zw); z_frag<1, 3>(bz[3][1], zw);
+        // independent accumulation chains are interleaved: the second MMA of a chain waits for the first
+        float d0[4], d1[4], dz[4];
+        mma_f16_first(d0, a[0][0], kOnesHalf2, kOnesHalf2);                   // row sums
+        mma_f16_first(d1, a[1][0], kOnesHalf2, kOnesHalf2);
+        mma_f16(d0, a[0][1], kOnesHalf2, kOnesHalf2);
+        mma_f16(d1, a[1][1], kOnesHalf2, kOnesHalf2);
+        rowt[0][0] = fmaf(cb, d0[0], rowt[0][0]);
+        rowt[0][1] = fmaf(cb, d0[2], rowt[0][1]);
+        rowt[1][0] = fmaf(cb, d1[0], rowt[1][0]);
+        rowt[1][1] = fmaf(cb, d1[2], rowt[1][1]);
+        const uint32_t ones[4] = {kOnesHalf2, kOnesHalf2, kOnesHalf2, kOnesHalf2};
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const uint32_t w = yb[(4 * gp + t) * kGroup] >> rp;
-            yr[rt] |= bytes_to_nibble(w) << (4 * t);
-            yr[rt] |= bytes_to_nibble(w >> 4) << (16 + 4 * t);
-          }
-          // column of Z: ranks gg + 8rr sit in the words of lanes 4*gg + tq at bits 8eq + 4qh + rr
-          const uint32_t* zb = p.zp + (((sg * g.RT + rt) * g.QT + qt) * 32) * kGroup + sub;
+        for (int nt = 0; nt < 4; ++nt) {
+          mma_f16_first(dz, ones, bz[nt][0][0], bz[nt][0][1]);                // column sums
+          mma_f16_first(d0, a[0][0], bz[nt][0][0], bz[nt][0][1]);
+          mma_f16_first(d1, a[1][0], bz[nt][0][0], bz[nt][0][1]);
+          mma_f16(dz, ones, bz[nt][1][0], bz[nt][1][1]);
+          mma_f16(d0, a[0][1], bz[nt][1][0], bz[nt][1][1]);
+          mma_f16(d1, a[1][1], bz[nt][1][0], bz[nt][1][1]);
+          colt[nt][0] = fmaf(cc, dz[0], colt[nt][0]);
+          colt[nt][1] = fmaf(cc, dz[1], colt[nt][1]);
 #pragma unroll
-          for (int gg = 0; gg < 8; ++gg) {
-            const uint32_t w = zb[(4 * gg + tq) * kGroup] >> zbase;
-            zc[rt] |= nibble_to_bytes(w & 0xFu) << gg;
+          for (int e = 0; e < 4; ++e) {
+            acc[0][nt][e] = fmaf(ca, d0[e], acc[0][nt][e]);
+            acc[1][nt][e] = fmaf(ca, d1[e], acc[1][nt][e]);
           }
-          ys += __popc(yr[rt]);
-          zs += __popc(zc[rt]);
         }
       }
-      rowterm = fmaf(cb, (float)ys, rowterm);
-      colterm = fmaf(cc, (float)zs, colterm);
-#pragma unroll
-      for (int pp = 0; pp < 32; ++pp) {
-        int core = 0;
-#pragma unroll
-        for (int rt = 0; rt < RT; ++rt) core += __popc(__shfl_sync(0xffffffffu, yr[rt], pp) & zc[rt]);
-        // int -> float on the FP32 pipe (core <= 64): 2^23 + core as a bit pattern, minus 2^23
-        acc[pp] = fmaf(ca, __int_as_float(0x4B000000 | core) - 8388608.f, acc[pp]);
-      }
     }
-    const int prow_max = min(32, g.P - 32 * pt);
-    const int ql = 32 * qt + lane;
-    const size_t at0 = (size_t)(i * g.P + 32 * pt) * ldw + (size_t)j * g.Q + ql;
-    WT* wrow = reinterpret_cast<WT*>(p.W) + at0;
-    WT* lrow = LO ? reinterpret_cast<WT*>(p.W_lo) + at0 : nullptr;
-    const bool col_ok = ql < g.Q;
+
+    // 32 x 32 entries: a lane holds two neighbouring columns of rows g8 + 8 (2 mt + h) in every 8-column tile
+    const int row0 = 32 * cur.pt + g8, col0 = 32 * cur.qt + 2 * t4;
+    const size_t at0 = ((size_t)cur.i * g.P + row0) * ldw + (size_t)cur.j * g.Q + col0;
+    WT* wp = reinterpret_cast<WT*>(p.W) + at0;
+    WT* lp = LO ? reinterpret_cast<WT*>(p.W_lo) + at0 : nullptr;
+    const bool whole = p.pairs && 32 * cur.pt + 32 <= g.P && 32 * cur.qt + 32 <= g.Q;
 #pragma unroll
-    for (int pp = 0; pp < 32; ++pp) {
-      const float rterm = __shfl_sync(0xffffffffu, rowterm, pp);
-      if (pp < prow_max && col_ok) {
-        const float w = (acc[pp] + colterm + rterm) * scale;
-        const WT wv = WType<DT>::cvt(w);
-        wrow[(size_t)pp * ldw] = wv;
-        if (LO) lrow[(size_t)pp * ldw] = WType<DT>::cvt(w - WType<DT>::back(wv));
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const size_t roff = (size_t)(16 * mt + 8 * h) * ldw;
+        const bool row_ok = whole || row0 + 16 * mt + 8 * h < g.P;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const float v0 = acc[mt][nt][2 * h] + rowt[mt][h] + colt[nt][0];
+          const float v1 = acc[mt][nt][2 * h + 1] + rowt[mt][h] + colt[nt][1];
+          WT* w = wp + roff + 8 * nt;
+          if (whole) {
+            const WT2 wv = WType<DT>::cvt2(v0, v1);
+            *reinterpret_cast<WT2*>(w) = wv;
+            if (LO)
+              *reinterpret_cast<WT2*>(lp + roff + 8 * nt) =
+                  WType<DT>::cvt2(v0 - WType<DT>::back(wv.x), v1 - WType<DT>::back(wv.y));
+          } else if (row_ok) {
+            const int col = col0 + 8 * nt;
+            if (col < g.Q) {
+              const WT w0 = WType<DT>::cvt(v0);
+              w[0] = w0;
+              if (LO) lp[roff + 8 * nt] = WType<DT>::cvt(v0 - WType<DT>::back(w0));
+            }
+            if (col + 1 < g.Q) {
+              const WT w1 = WType<DT>::cvt(v1);
+              w[1] = w1;
+              if (LO) lp[roff + 8 * nt + 1] = WType<DT>::cvt(v1 - WType<DT>::back(w1));
+            }
+          }
+        }
       }
-    }
+
+    cur = nxt;
+    i = ni;
+    tj = ntj;
+    have = have_next;
   }
 }
 
 template <int RT>
-static void reconstruct_dispatch(const ReconParams& p, int blocks, cudaStream_t st) {
+static void reconstruct_dispatch(const ReconParams& p, dim3 blocks, cudaStream_t st) {
   const int threads = kReconWarps * 32;
   const bool lo = p.W_lo != nullptr;
   if (p.w_dtype == BQQ_F32) bqq_reconstruct_kernel<RT, BQQ_F32, false><<<blocks, threads, 0, st>>>(p);
@@ -161,12 +332,15 @@ int reconstruct_launch(const BqqLayer* L, void* W, void* W_lo, int w_dtype, floa
   p.zp = L->zplanes; p.yp = L->yplanes;
   p.a = L->a; p.b = L->b; p.c = L->c; p.d = L->d; p.coef_dtype = L->coef_dtype;
   p.W = W; p.W_lo = W_lo; p.scale = scale; p.bound_parts = bound_parts; p.w_dtype = w_dtype;
-  p.total_tasks = (long long)p.g.rw * p.g.cw * p.g.PT * p.g.QT;
-  long long blocks = (p.total_tasks + kReconWarps - 1) / kReconWarps;
-  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  p.tasks_per_row = p.g.cw * p.g.PT * p.g.QT;      // in_features <= 2^30 keeps this far below 2^31
+  const uintptr_t pair_mask = 2 * (uintptr_t)dtype_size(w_dtype) - 1;
+  p.pairs = (p.g.Q % 2 == 0 && ((uintptr_t)W & pair_mask) == 0 && ((uintptr_t)W_lo & pair_mask) == 0) ? 1 : 0;
+  // resident warps walk the blocks: 4 CTAs per SM on 148 SMs
+  const long long tasks = (long long)p.tasks_per_row * p.g.rw;
+  const dim3 blocks((unsigned)std::min<long long>((tasks + kReconWarps - 1) / kReconWarps, 148LL * 4));
   if (w_dtype == BQQ_F32 && W_lo) return BQQ_ERR_UNSUPPORTED;     // a second part only exists for 16-bit types
-  if (p.g.RT == 1) reconstruct_dispatch<1>(p, (int)blocks, st);
-  else reconstruct_dispatch<2>(p, (int)blocks, st);
+  if (p.g.RT == 1) reconstruct_dispatch<1>(p, blocks, st);
+  else reconstruct_dispatch<2>(p, blocks, st);
   return launch_status();
 }
 

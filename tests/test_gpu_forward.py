@@ -150,6 +150,25 @@ def test_get_weight_gpu():
         assert np.abs(Wb.float().cpu().numpy() - Wref).max() <= 2 ** -8 * np.abs(Wref).max()
 
 
+@pytest.mark.parametrize('shape', DECODE_SHAPES + [(2, 3, 4, 9, 7, 5), (2, 2, 3, 33, 31, 40)])
+def test_get_weight_all_geometries(shape):
+    """Dense weight from the planes for padded, ragged, odd-width and two-rank-block patches, in every element type."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, P, Q, r = shape
+    Y, Z, A, _, _ = synth_layer(bw, rw, cw, P, Q, r, 1, seed=21)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    a, b, c, d = O.split_coefficients(A.numpy())
+    Wref = O.dense_weight(Y.numpy(), Z.numpy(), a, b, c, d)
+    scale = max(1.0, np.abs(Wref).max())
+    W = bq.get_weight(torch.float32)
+    assert tuple(W.shape) == (rw * P, cw * Q)
+    assert np.abs(W.cpu().numpy() - Wref).max() <= 1e-5 * scale
+    for dt, eps in ((torch.bfloat16, 2 ** -8), (torch.float16, 2 ** -10)):
+        Wd = bq.get_weight(dt)
+        assert Wd.dtype == dt
+        assert np.abs(Wd.float().cpu().numpy() - Wref).max() <= eps * scale
+
+
 def test_decode_is_deterministic_and_workspace_reusable():
     from bqq_b200.bqq_modules import BinaryQuadratic
     Y, Z, A, _, X = synth_layer(2, 32, 64, 32, 32, 32, 4, seed=9)
