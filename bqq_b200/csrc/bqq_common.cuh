@@ -138,7 +138,7 @@ int decode_launches(const BqqDims* dims, int M);   // kernels per decode call: 1
 size_t decode_counter_bytes();   // leading part of the decode workspace that must start zeroed
 int reconstruct_launch(const BqqLayer* layer, void* W, void* W_lo, int w_dtype, float scale,
                        const float* bound_parts, cudaStream_t stream);
-int coef_bound_launch(const BqqLayer* layer, float* bound_parts, cudaStream_t stream);
+int coef_bound_launch(const BqqLayer* layer, float* bound_parts, cudaStream_t stream);   // bound_parts zero on entry
 int prefill_launch(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                    int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t prefill_workspace_bytes(const BqqDims* dims, int M);

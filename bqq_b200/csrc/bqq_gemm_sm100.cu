@@ -263,8 +263,8 @@ __global__ void stage_x_kernel(const void* __restrict__ x, int x_dtype, int64_t 
 // so nothing overflows and every bf16 value in range converts exactly); row_unscale[m] = 1 / scale.
 // One block per row; with `vec` a thread moves 8 values per access and keeps its first kStageKeep
 // accesses in registers, so rows up to 8 * kStageKeep * blockDim.x values are read once.
-constexpr int kStageThreads = 256;
-constexpr int kStageKeep = 2;
+constexpr int kStageThreads = 128;
+constexpr int kStageKeep = 4;
 __global__ void __launch_bounds__(kStageThreads)
 stage_x_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int M, int K,
                            __half* __restrict__ out, float* __restrict__ row_unscale, int vec) {
@@ -410,7 +410,7 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   uint16_t* xlo = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(xhi) + up256((size_t)M * K * 2));
   float* bound_parts = reinterpret_cast<float*>(wsb + 16);
 
-  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return BQQ_ERR_CUDA;
+  if (cudaMemsetAsync(status, 0, 32, st) != cudaSuccess) return BQQ_ERR_CUDA;   // status word and bound parts
 
   // 1. dense W into scratch.  fp16 and bf16 activations use one fp16 W scaled by a power of two
   //    (bf16 rows are re-staged as scaled fp16, exact); fp32 activations use the bf16 hi + lo pair.

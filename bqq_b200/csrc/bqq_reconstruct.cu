@@ -344,7 +344,7 @@ int reconstruct_launch(const BqqLayer* L, void* W, void* W_lo, int w_dtype, floa
   return launch_status();
 }
 
-// bound_parts[0] = max(|a|+|b|+|c|), bound_parts[1] = max|d| (both must be zero on entry)
+// bound_parts[0] = max(|a|+|b|+|c|), bound_parts[1] = max|d| (both must be zero on entry: the caller clears them)
 __global__ void coef_bound_kernel(const void* a, const void* b, const void* c, const void* d, int dt, size_t nabc,
                                   size_t nd, float* bound_parts) {
   float m0 = 0.f, m1 = 0.f;
@@ -357,7 +357,14 @@ __global__ void coef_bound_kernel(const void* a, const void* b, const void* c, c
     m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
     m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
   }
-  if ((threadIdx.x & 31) == 0) {      // non-negative floats order like ints
+  // one pair of atomics per block: the warps' maxima meet in shared memory first
+  __shared__ float part[2][8];
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) { part[0][warp] = m0; part[1][warp] = m1; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) { m0 = fmaxf(m0, part[0][w]); m1 = fmaxf(m1, part[1][w]); }
+    // non-negative floats order like ints
     atomicMax(reinterpret_cast<int*>(bound_parts), __float_as_int(m0));
     atomicMax(reinterpret_cast<int*>(bound_parts) + 1, __float_as_int(m1));
   }
@@ -365,9 +372,8 @@ __global__ void coef_bound_kernel(const void* a, const void* b, const void* c, c
 
 int coef_bound_launch(const BqqLayer* L, float* bound_parts, cudaStream_t st) {
   Geom g(L->dims);
-  if (cudaMemsetAsync(bound_parts, 0, 8, st) != cudaSuccess) return BQQ_ERR_CUDA;
   const size_t nabc = (size_t)g.bw * g.rw * g.cw, nd = (size_t)g.rw * g.cw;
-  int blocks = (int)((nabc + 255) / 256 < 592 ? (nabc + 255) / 256 : 592);
+  int blocks = (int)((nabc + 255) / 256 < 296 ? (nabc + 255) / 256 : 296);
   coef_bound_kernel<<<blocks, 256, 0, st>>>(L->a, L->b, L->c, L->d, L->coef_dtype, nabc, nd, bound_parts);
   return launch_status();
 }
