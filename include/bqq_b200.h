@@ -320,10 +320,11 @@ int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtyp
 
 /*
  * Dense weight W [rw*P, cw*Q] row-major in element type w_dtype: the value of
- * BinaryQuadratic.get_weight (src/bqq_modules.py:48-55), built with AND +
- * popcount like reconstruct_W_kernel (src/bqq_cuda.cu:198-246) but with
- * coalesced row-major stores.  `scale` multiplies every entry (1.0f for the
- * plain weight).
+ * BinaryQuadratic.get_weight (src/bqq_modules.py:48-55).  Replaces
+ * reconstruct_W_kernel (src/bqq_cuda.cu:198-246): the per-entry counts
+ * popc(Yrow & Zcol) are formed as exact small-integer products on the
+ * tensor cores, one 32x32 block per warp, and stored row-major.  `scale`
+ * multiplies every entry (1.0f for the plain weight).
  */
 int bqq_reconstruct_weight(const BqqLayer* layer, void* W, int w_dtype, float scale, void* stream);
 

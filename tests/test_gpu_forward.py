@@ -117,6 +117,24 @@ def test_prefill_fp32_output_tolerance():
     assert O.max_rel_err(y.cpu().numpy(), ref) < TOL
 
 
+def test_prefill_row_strided_bf16_inputs():
+    """bf16 rows longer than one pass of the staging block keeps in registers, read through row-strided views whose
+    pitch does (16-byte accesses) and does not (2-byte accesses) allow the vector path: all three give the same bits."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    bw, rw, cw, P, Q, r, M = 2, 2, 144, 32, 32, 32, 40
+    Y, Z, A, _, X = synth_layer(bw, rw, cw, P, Q, r, M, seed=11, x_dtype=torch.bfloat16)
+    K = cw * Q
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    y = _run(bq, X.cuda())
+    assert O.max_rel_err(y.float().cpu().numpy(), oracle_forward_t(Y, Z, A, None, X)) < TOL + 2 ** -8
+    for pad in (16, 12):
+        big = torch.zeros(M, K + pad, dtype=torch.bfloat16, device='cuda')
+        big[:, :K] = X.cuda()
+        view = big[:, :K]
+        assert view.stride(0) == K + pad
+        assert torch.equal(_run(bq, view), y)
+
+
 def test_leading_dims_and_strides():
     from bqq_b200.bqq_modules import BinaryQuadratic
     Y, Z, A, _, _ = synth_layer(2, 4, 4, 32, 32, 32, 1, seed=3)
