@@ -7,7 +7,7 @@
 // split into bf16 hi + lo the same way (passes hi*hi, hi*lo, lo*hi).  Replaces reconstruct_W_kernel + torch::mm of
 // the reference (neural_network_compression/src/bqq_cuda.cu:198-246, 367-383).
 //
-// GEMM kernel, one 128 x BN output tile per CTA, 6 warps:
+// GEMM kernel, one 128 x BN output tile per CTA (BN = 256, 128, 64 or 32), 6 warps:
 //   warp 0   TMA producer: 4-stage ring of {A 128x64, B BNx64} 16-bit tiles,
 //            128-byte swizzle, completion on mbarriers
 //   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN,
@@ -451,7 +451,12 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   }
   const bool split_x = x_dtype == BQQ_F32;
 
-  const int BN = (N >= 256) ? 256 : 128;
+  // widest tile that still gives about one CTA per SM: small batches are bound by how many SMs stream W
+  int BN = 32;
+  for (int cand = 256; cand >= 64; cand >>= 1) {
+    const long long ctas = (long long)((N + cand - 1) / cand) * ((M + kBM - 1) / kBM);
+    if (ctas >= 118) { BN = cand; break; }
+  }
   CUtensorMap ma0, ma1, mb;
   rc = make_map(&ma0, a_ptr, !f16, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, kBM);
   if (rc) return rc;
@@ -477,7 +482,12 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   // instruction descriptor: fp32 accumulate, A and B in the same 16-bit format, both K-major
   const uint32_t fmt = f16 ? 0u : 1u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-  return BN == 256 ? launch_gemm<256>(ma0, ma1, mb, p, st) : launch_gemm<128>(ma0, ma1, mb, p, st);
+  switch (BN) {
+    case 256: return launch_gemm<256>(ma0, ma1, mb, p, st);
+    case 128: return launch_gemm<128>(ma0, ma1, mb, p, st);
+    case 64: return launch_gemm<64>(ma0, ma1, mb, p, st);
+    default: return launch_gemm<32>(ma0, ma1, mb, p, st);
+  }
 }
 
 }  // namespace bqq

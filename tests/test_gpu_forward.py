@@ -95,6 +95,18 @@ def test_prefill_against_oracle(shape, M):
         assert err < TOL + out_round, (dt, err)
 
 
+@pytest.mark.parametrize('M', [1024, 512, 256, 128, 40])
+def test_prefill_every_tile_width(M):
+    """4096 outputs: the GEMM picks its tile width (256, 128, 64, 32 columns) by the number of tiles the batch gives."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(2, 128, 8, 32, 32, 32, M, seed=M, x_dtype=torch.bfloat16, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    y = _run(bq, X.cuda())
+    assert O.max_rel_err(y.float().cpu().numpy(), oracle_forward_t(Y, Z, A, bias, X)) < TOL + 2 ** -8
+    y32 = _run(bq, X.float().cuda())
+    assert O.max_rel_err(y32.cpu().numpy(), oracle_forward_t(Y, Z, A, bias, X)) < TOL
+
+
 def test_prefill_fp32_output_tolerance():
     """Config-3-like contraction (K = 4096) with fp32 outputs so only compute error remains."""
     from bqq_b200.bqq_modules import BinaryQuadratic
