@@ -24,7 +24,8 @@ EXPORTS = [
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
     'bqq_decode_launches', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
-    'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc',
+    'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc', 'bqq_noalloc_status',
+    'bqq_decode_status', 'bqq_prefill_status',
     'bqq_peer_region_bytes', 'bqq_peer_alloc', 'bqq_peer_open', 'bqq_peer_close', 'bqq_peer_free',
     'bqq_peer_gather', 'bqq_peer_status', 'bqq_forward_decode_gathered',
 ]
@@ -54,7 +55,7 @@ PEER_HANDLE_BYTES = 64
 
 class BqqPeerGroup(C.Structure):
     _fields_ = [('rank', C.c_int32), ('world', C.c_int32), ('regions', C.c_void_p * MAX_PEERS),
-                ('gather_bytes', C.c_uint64)]
+                ('gather_bytes', C.c_uint64), ('wait_cycles', C.c_uint64)]
 
 
 def _load():
@@ -99,6 +100,9 @@ def _load():
                                             C.POINTER(BqqPeerGroup), vp, i64, vp, sz, vp]),
         'bqq_noalloc_scratch_bytes': (sz, []),
         'bqq_forward_decode_noalloc': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp]),
+        'bqq_noalloc_status': (i32, [vp]),
+        'bqq_decode_status': (i32, [vp, vp]),
+        'bqq_prefill_status': (i32, [vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

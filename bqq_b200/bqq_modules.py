@@ -3,10 +3,14 @@
 Same names, constructor arguments, attributes and state_dict layout as the
 reference module neural_network_compression/src/bqq_modules.py, so that
 saved whole-model pickles (which record the class path
-`bqq_modules.BinaryQuadratic`), `replace_linear_with_bqq`
-(lm/build_bqq_model.py:79-112) and the `__new__`-and-fill construction of
-lm/benchmark_inference.py:24-41 keep working.  Put this package's directory on
-sys.path in place of the reference's `src/`, or call `bqq_b200.install()`.
+`bqq_modules.BinaryQuadratic`), the reference's own lm/build_bqq_model.py
+(it imports BinaryQuadratic, PackedBinaryQuadratic, PartialBQQLinear,
+get_matrices, merge_binary_quadratic, merge_binaryquadratic_recursive and
+pack_binaryquadratic_model from here, lm/build_bqq_model.py:57-65) and the
+`__new__`-and-fill construction of lm/benchmark_inference.py:24-41 keep
+working.  Put this package's directory on sys.path in place of the reference's
+`src/`, or call `bqq_b200.install()`.  The {-1,+1} vision layers of the
+reference (BQQLinear and friends) are not implemented; see the end of the file.
 
 What differs is only how forward() computes: instead of rebuilding the dense
 weight with torch ops on every call (src/bqq_modules.py:34-46) it calls the
@@ -30,19 +34,44 @@ _DTYPE_CODE = {torch.float32: _cabi.F32, torch.bfloat16: _cabi.BF16, torch.float
 # workspace cache: one growing buffer per (device, stream, kind)
 # ---------------------------------------------------------------------------
 _WORKSPACES: dict = {}
+_RETIRED_WORKSPACES: list = []
 
 
 def _workspace(device: torch.device, kind: str, nbytes: int) -> torch.Tensor:
     """Scratch buffer for the kernels.  Decode scratch must start zeroed (the
     kernel leaves it zeroed); calls that share a buffer must not overlap on the
-    GPU, hence one buffer per stream."""
+    GPU, hence one buffer per stream.
+
+    A buffer that has to grow is replaced, but the old one is kept alive for the life of the
+    process: a CUDA graph captured earlier holds its raw address and would otherwise read and
+    write memory that the allocator has handed to another tensor.  Growth while the stream is
+    being captured is refused (the allocation would land in the capture's private pool)."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream, kind)
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                'bqq_b200: the scratch buffer of this stream has to grow during a CUDA graph capture; run the '
+                'largest layer / batch of the captured region once before capturing')
+        if buf is not None:
+            _RETIRED_WORKSPACES.append(buf)
         size = max(int(nbytes), 256)
         buf = torch.zeros(size, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = buf
     return buf
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a bounded device-side wait gave up in any forward that used this
+    process's scratch buffers on `device` (all devices when None); the outputs of such a forward
+    are invalid.  The kernels never hang on such a wait: they record it and return."""
+    index = None if device is None else torch.device(device).index
+    for (dev, stream, kind), buf in list(_WORKSPACES.items()):
+        if index is not None and dev != index:
+            continue
+        with torch.cuda.device(dev):
+            fn = lib.bqq_prefill_status if kind.endswith('prefill') else lib.bqq_decode_status
+            check(fn(buf.data_ptr(), stream), f'bqq_b200 {kind} scratch on cuda:{dev}')
 
 
 class _PackedState:
@@ -157,7 +186,11 @@ class _BqqForwardMixin:
     def forward(self, X):
         self._check_inference_only(X)
         if X.dtype not in _DTYPE_CODE:
-            raise RuntimeError(f'bqq_b200: unsupported activation dtype {X.dtype} (fp32, bf16, fp16 only)')
+            # the reference computes in whatever float type X has (src/bqq_modules.py:35); the kernels
+            # take fp32 / bf16 / fp16, so any other float type (fp64) goes through fp32 and back
+            if not X.is_floating_point():
+                raise RuntimeError(f'bqq_b200: unsupported activation dtype {X.dtype} (floating point only)')
+            return self.forward(X.to(torch.float32)).to(X.dtype)
         st = self._ensure_packed()
         device = st.zplanes.device
         in_f = self.col_width * self.z_col
@@ -400,6 +433,18 @@ class _BqqForwardMixin:
         return W
 
 
+def _dense_weight(Y, Z, a, b, c, d, dtype):
+    """W [rw*P, cw*Q] from the factors with torch ops (src/bqq_modules.py:37-42):
+    sum over bit layers of a*YZ + b*(Y1)1' + c*1(1'Z), plus d, patches laid out row-major.
+    Differentiable in a, b, c, d; used where autograd or a CPU tensor is wanted, never by forward()."""
+    Yd, Zd = Y.to(dtype), Z.to(dtype)
+    per_bit = (a.to(dtype) * (Yd @ Zd) + b.to(dtype) * Yd.sum(-1, keepdim=True)
+               + c.to(dtype) * Zd.sum(-2, keepdim=True))
+    tiles = per_bit.sum(0) + d.to(dtype)                      # [rw, cw, P, Q]
+    rw, cw, P, Q = tiles.shape
+    return tiles.transpose(1, 2).reshape(rw * P, cw * Q)
+
+
 # ---------------------------------------------------------------------------
 # BinaryQuadratic
 # ---------------------------------------------------------------------------
@@ -441,11 +486,7 @@ class BinaryQuadratic(_BqqForwardMixin, nn.Module):
         it is evaluated with torch ops (not a forward path)."""
         if self.Y.is_cuda and dtype in _DTYPE_CODE:
             return self._weight_gpu(dtype)
-        Yf, Zf = self.Y.to(dtype), self.Z.to(dtype)
-        core = Yf @ Zf
-        W = (self.a.to(dtype) * core + self.b.to(dtype) * Yf.sum(-1, keepdim=True)
-             + self.c.to(dtype) * Zf.sum(-2, keepdim=True)).sum(0) + self.d.to(dtype)
-        return W.permute(0, 2, 1, 3).reshape(self.row_width * self.y_row, self.col_width * self.z_col)
+        return _dense_weight(self.Y, self.Z, self.a, self.b, self.c, self.d, dtype)
 
     def unpack_planes(self):
         """Bit planes back to bool Y, Z (bit-exact round-trip check)."""
@@ -658,14 +699,67 @@ def get_matrices(patch_list, bit_width):
     return A, Y, Z
 
 
-def replace_linear_with_bqq(model: nn.Module, load_patches, bit_width: int, prefix: str = '',
+def _patch_loader(source):
+    """`source` of replace_linear_with_bqq -> function weight_key -> patch list.
+
+    A callable is used as it is.  A directory is read in the reference's on-disk formats
+    (lm/compressed_data.py:40-58, 152-191): `<dir>/_consolidated/<weight_key>.pth` holds the whole
+    list of patch dicts of one tensor; otherwise the files `<dir>/<weight_key>_row*.pth` each hold a
+    list of patch dicts and are concatenated in sorted order."""
+    if callable(source):
+        return source
+    import os
+    root = os.fspath(source)
+    if not os.path.isdir(root):
+        raise FileNotFoundError(f'bqq_b200: patch directory does not exist: {root}')
+    merged_dir = os.path.join(root, '_consolidated')
+    per_patch: dict = {}
+    for entry in os.scandir(root):
+        if entry.name.endswith('.pth') and '_row' in entry.name:
+            per_patch.setdefault(entry.name[:-4].rsplit('_row', 1)[0], []).append(entry.path)
+
+    def load(weight_key):
+        merged = os.path.join(merged_dir, weight_key + '.pth')
+        if os.path.exists(merged):
+            return torch.load(merged, weights_only=False, map_location='cpu')
+        patches = []
+        for path in sorted(per_patch.get(weight_key, ())):
+            patches.extend(torch.load(path, weights_only=False, map_location='cpu'))
+        return patches
+
+    return load
+
+
+def replace_linear_with_bqq(model: nn.Module, weights_dir, bit_width: int, prefix: str = '',
+                            device=None, show_tqdm: bool = False, patch_index=None,
                             planes_only: bool = False) -> nn.Module:
-    """Walk the module tree and replace nn.Linear by BinaryQuadratic, skipping
-    any name that contains 'head', as lm/build_bqq_model.py:79-112 does.
-    `load_patches(weight_key)` returns the patch list of `<name>.weight` or None
-    (the reference reads it from its consolidated patch files).  With
-    `planes_only` the layers are PlaneBinaryQuadratic, packed patch by patch
-    without the dense Y / Z tensors."""
+    """Walk the module tree and replace nn.Linear by BinaryQuadratic, skipping any name that
+    contains 'head'; argument order and meaning follow lm/build_bqq_model.py:79-112.
+
+    `weights_dir` is the directory of patch files written by the quantiser (see _patch_loader for
+    the two layouts) or, as an extension, a callable `weight_key -> patch list`.  `patch_index`
+    (the reference's name -> path(s) dictionary) is honoured when given; `device` and `show_tqdm`
+    are accepted for call compatibility (patches are read on the host; no progress bar is drawn).
+    With `planes_only` the new layers are PlaneBinaryQuadratic, packed patch by patch without the
+    dense Y / Z tensors.  Linears without patches are left in place, as in the reference."""
+    if patch_index is not None and not callable(weights_dir):
+        index = patch_index
+
+        def load_patches(weight_key):
+            entry = index.get(weight_key)
+            if entry is None:
+                return []
+            paths = [entry] if not isinstance(entry, (list, tuple)) else list(entry)
+            out = []
+            for path in paths:
+                out.extend(torch.load(path, weights_only=False, map_location='cpu'))
+            return out
+    else:
+        load_patches = _patch_loader(weights_dir)
+    return _replace_linears(model, load_patches, bit_width, prefix, planes_only)
+
+
+def _replace_linears(model, load_patches, bit_width, prefix, planes_only):
     for name, module in list(model.named_children()):
         full = f'{prefix}.{name}' if prefix else name
         if 'head' in full:
@@ -681,8 +775,170 @@ def replace_linear_with_bqq(model: nn.Module, load_patches, bit_width: int, pref
                 A, Y, Z = get_matrices(patches, bit_width)
                 setattr(model, name, BinaryQuadratic(Y, Z, A, bias=module.bias))
         else:
-            replace_linear_with_bqq(module, load_patches, bit_width, prefix=full, planes_only=planes_only)
+            _replace_linears(module, load_patches, bit_width, full, planes_only)
     return model
+
+
+# ---------------------------------------------------------------------------
+# Layers and helpers of the reference's quantisation workflows (not on the forward path)
+# ---------------------------------------------------------------------------
+
+def _binaryquadratic_from_parts(Y, Z, a, b, c, d, bias):
+    """BinaryQuadratic from already split coefficients, without the (Y, Z, A) constructor - the
+    route lm/benchmark_inference.py:30-40 and src/bqq_modules.py:416-432 take."""
+    layer = BinaryQuadratic.__new__(BinaryQuadratic)
+    nn.Module.__init__(layer)
+    (layer.bit_width, layer.row_width, layer.col_width, layer.y_row, layer.inter_dimension) = Y.shape
+    layer.z_col = Z.shape[-1]
+    layer.register_buffer('Y', Y.clone() if Y.dtype == torch.bool else Y > 0.5)
+    layer.register_buffer('Z', Z.clone() if Z.dtype == torch.bool else Z > 0.5)
+    for name, value in (('a', a), ('b', b), ('c', c), ('d', d)):
+        setattr(layer, name, nn.Parameter(value.detach().clone()))
+    layer.bias = nn.Parameter(bias.detach().clone()) if bias is not None else None
+    return layer
+
+
+class PartialBQQLinear(nn.Module):
+    """Linear layer whose patches are quantised one group at a time during block-wise training
+    (src/bqq_modules.py:246-432; used by lm/blockwise_quant.py:540-632 and imported by
+    lm/build_bqq_model.py:57-65).
+
+    State, names as in the reference so that its pickles and training loops work: `float_weight`
+    [out, in] fp32 (trainable, stands for every patch not yet quantised), `bias_param`, bool buffer
+    `quantized_mask` [rw, cw], and - created by the first quantize_patch, when the rank is known -
+    bool buffers `Y`, `Z` and parameters `a, b, c, d` shaped as in BinaryQuadratic.
+
+    This is a training-time layer: forward() is plain differentiable torch code (W is assembled per
+    call; gradients reach a..d through the quantised patches and float_weight through the others).
+    It is not a forward path of the CUDA library; to_binaryquadratic() hands the finished layer to
+    it."""
+
+    def __init__(self, weight: torch.Tensor, bias, group_size: int, bit_width: int):
+        super().__init__()
+        out_f, in_f = weight.shape
+        for what, n in (('out_features', out_f), ('in_features', in_f)):
+            if n % group_size:
+                raise ValueError(f'{what}={n} is not divisible by group_size={group_size}.')
+        self.group_size, self.bit_width = group_size, bit_width
+        self.row_width, self.y_row = out_f // group_size, group_size
+        self.col_width, self.z_col = in_f // group_size, group_size
+        self.inter_dimension = None                      # known once the first patch arrives
+        self.float_weight = nn.Parameter(weight.detach().clone().float())
+        self.bias_param = nn.Parameter(bias.detach().clone().float()) if bias is not None else None
+        self.register_buffer('quantized_mask', torch.zeros(self.row_width, self.col_width, dtype=torch.bool))
+
+    def _init_bqq_tensors(self, inter_dimension: int) -> None:
+        dev = self.float_weight.device
+        grid = (self.bit_width, self.row_width, self.col_width)
+        self.inter_dimension = inter_dimension
+        self.register_buffer('Y', torch.zeros(*grid, self.y_row, inter_dimension, dtype=torch.bool, device=dev))
+        self.register_buffer('Z', torch.zeros(*grid, inter_dimension, self.z_col, dtype=torch.bool, device=dev))
+        for name in 'abc':
+            setattr(self, name, nn.Parameter(torch.zeros(*grid, 1, 1, device=dev)))
+        self.d = nn.Parameter(torch.zeros(self.row_width, self.col_width, 1, 1, device=dev))
+
+    def quantize_patch(self, i: int, j: int, A_ij, Y_ij, Z_ij) -> None:
+        """Patch (i, j) becomes quantised: A_ij [bw, 4], Y_ij [bw, P, r], Z_ij [bw, r, Q]."""
+        if self.inter_dimension is None:
+            self._init_bqq_tensors(Y_ij.shape[-1])
+        dev = self.float_weight.device
+        with torch.no_grad():
+            self.Y[:, i, j] = (Y_ij > 0.5).to(dev)
+            self.Z[:, i, j] = (Z_ij > 0.5).to(dev)
+            for n, name in enumerate('abc'):
+                getattr(self, name).data[:, i, j, 0, 0] = A_ij[:, n].to(dev)
+            self.d.data[i, j, 0, 0] = A_ij[:, 3].sum().to(dev)      # one offset per patch, as BinaryQuadratic
+            self.quantized_mask[i, j] = True
+
+    def _bqq_weight(self, dtype):
+        return _dense_weight(self.Y, self.Z, self.a, self.b, self.c, self.d, dtype)
+
+    def forward(self, X):
+        dtype, dev = X.dtype, self.float_weight.device
+        none_done = self.inter_dimension is None or not bool(self.quantized_mask.any())
+        if none_done:
+            W = self.float_weight.to(dtype)
+        else:
+            W = self._bqq_weight(dtype)
+            if not bool(self.quantized_mask.all()):
+                per_entry = self.quantized_mask.repeat_interleave(self.y_row, 0).repeat_interleave(self.z_col, 1)
+                W = torch.where(per_entry, W, self.float_weight.to(dtype))
+        out = X.to(dev) @ W.T
+        if self.bias_param is not None:
+            out = out + self.bias_param.to(dtype=dtype, device=dev)
+        return out
+
+    def to_binaryquadratic(self) -> BinaryQuadratic:
+        """The finished layer as this package's BinaryQuadratic; raises while patches are missing."""
+        missing = int((~self.quantized_mask).sum())
+        if missing:
+            raise RuntimeError(f'to_binaryquadratic() called but {missing} patches are still unquantized')
+        return _binaryquadratic_from_parts(self.Y, self.Z, self.a.data, self.b.data, self.c.data, self.d.data,
+                                           self.bias_param.data if self.bias_param is not None else None)
+
+
+def merge_binary_quadratic(diff_layer: BinaryQuadratic, quant_layer: BinaryQuadratic) -> BinaryQuadratic:
+    """Bit-depth extension: the bit layers of `diff_layer` (fitted to the residual) are appended to
+    those of `quant_layer`; d adds up; the bias is quant_layer's (src/bqq_modules.py:449-463).
+
+    The reference builds the result through the (Y, Z, A) constructor and concatenates a 4-D with a
+    5-D tensor on the way, so its version raises for every input.  This one returns the layer that
+    code describes: bit layers [quant..., diff...] and d = quant.d + diff.d."""
+    if (quant_layer.Y.shape[1:] != diff_layer.Y.shape[1:]) or (quant_layer.Z.shape[1:] != diff_layer.Z.shape[1:]):
+        raise ValueError('merge_binary_quadratic: layers differ in patch grid or patch geometry')
+    cat = lambda name: torch.cat([getattr(quant_layer, name).data, getattr(diff_layer, name).data], dim=0)  # noqa: E731
+    return _binaryquadratic_from_parts(torch.cat([quant_layer.Y, diff_layer.Y], 0),
+                                       torch.cat([quant_layer.Z, diff_layer.Z], 0),
+                                       cat('a'), cat('b'), cat('c'), quant_layer.d.data + diff_layer.d.data,
+                                       quant_layer.bias.data if quant_layer.bias is not None else None)
+
+
+def merge_binaryquadratic_recursive(model_q: nn.Module, model_d: nn.Module, prefix=''):
+    """Merge every BinaryQuadratic of `model_d` into its namesake in `model_q`, in place
+    (src/bqq_modules.py:466-479)."""
+    for (name_q, child_q), (name_d, child_d) in zip(list(model_q.named_children()), list(model_d.named_children())):
+        if name_q != name_d:
+            raise AssertionError(f'Module name mismatch: {name_q} != {name_d}')
+        full = f'{prefix}.{name_q}' if prefix else name_q
+        if isinstance(child_q, BinaryQuadratic) and isinstance(child_d, BinaryQuadratic):
+            setattr(model_q, name_q, merge_binary_quadratic(child_d, child_q))
+        else:
+            merge_binaryquadratic_recursive(child_q, child_d, prefix=full)
+    return model_q
+
+
+# The {-1,+1} layers of the reference's vision workflow (src/bqq_modules.py:514-736: transform_A,
+# SymQuantSTE, BQQLinear, BQQLinearInference) are a different layer family with its own training
+# code and are not implemented here.  So that scripts which import them beside BinaryQuadratic
+# still run, they are taken from a checkout of the reference when BQQ_REFERENCE_SRC names its
+# `src` directory; without it the import fails with a message that says so.
+_REFERENCE_ONLY = ('transform_A', 'SymQuantSTE', 'BQQLinear', 'BQQLinearInference')
+_reference_module = None
+
+
+def _load_reference_module():
+    global _reference_module
+    if _reference_module is None:
+        import importlib.util
+        import os
+        src = os.environ.get('BQQ_REFERENCE_SRC', '')
+        path = os.path.join(src, 'bqq_modules.py')
+        if not src or not os.path.exists(path):
+            raise ImportError(
+                'bqq_b200: ' + ', '.join(_REFERENCE_ONLY) + ' belong to the reference\'s {-1,+1} vision layers, '
+                'which this package does not implement; set BQQ_REFERENCE_SRC to the reference\'s '
+                'neural_network_compression/src directory to have them loaded from there')
+        spec = importlib.util.spec_from_file_location('_bqq_reference_modules', path)
+        module = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(module)
+        _reference_module = module
+    return _reference_module
+
+
+def __getattr__(name):
+    if name in _REFERENCE_ONLY:
+        return getattr(_load_reference_module(), name)
+    raise AttributeError(f'module {__name__!r} has no attribute {name!r}')
 
 
 def shard_rows(bq: BinaryQuadratic, rank: int, world: int) -> BinaryQuadratic:

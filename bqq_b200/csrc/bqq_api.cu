@@ -25,10 +25,9 @@ static int check_io(const BqqLayer* L, const void* x, int x_dtype, int M, int64_
   return BQQ_OK;
 }
 
-// bqq_forward_decode, optionally with the peer stores of bqq_forward_decode_gathered (not exported in the header)
-int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
-                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
-                            const BqqFusion* fusion = nullptr) {
+// Argument checks of the decode entry points (nothing is enqueued); not exported in the header.
+int bqq_decode_check_args(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                          int64_t ldy, const BqqFusion* fusion) {
   int rc = check_layer(layer);
   if (rc) return rc;
   rc = check_io(layer, x, x_dtype, M, ldx, y, y_dtype, ldy);
@@ -43,6 +42,15 @@ int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, i
     if (fusion->residual && (!dtype_size(fusion->residual_dtype) || fusion->ld_residual < g.out_features()))
       return dtype_size(fusion->residual_dtype) ? BQQ_ERR_BAD_SHAPE : BQQ_ERR_DTYPE;
   }
+  return BQQ_OK;
+}
+
+// bqq_forward_decode, optionally with the peer stores of bqq_forward_decode_gathered (not exported in the header)
+int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                            int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
+                            const BqqFusion* fusion = nullptr) {
+  const int rc = bqq_decode_check_args(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, fusion);
+  if (rc) return rc;
   return decode_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
                        (cudaStream_t)stream, peer, fusion);
 }
@@ -121,6 +129,27 @@ int bqq_forward(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_
   if (M <= BQQ_DECODE_MAX_M)
     return bqq_forward_decode(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
   return bqq_forward_prefill(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes, stream);
+}
+
+// One 32-bit word of device memory, read back after synchronising the stream.
+static int read_status_word(const void* word, void* stream) {
+  unsigned st = 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(&st, word, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+    cudaGetLastError();
+    return BQQ_ERR_CUDA;
+  }
+  return st ? BQQ_ERR_TIMEOUT : BQQ_OK;
+}
+
+int bqq_decode_status(const void* workspace, void* stream) {
+  if (!workspace) return BQQ_ERR_NULL;
+  return read_status_word(reinterpret_cast<const char*>(workspace) + decode_counter_bytes() - 4, stream);
+}
+
+int bqq_prefill_status(const void* workspace, void* stream) {
+  if (!workspace) return BQQ_ERR_NULL;
+  return read_status_word(workspace, stream);
 }
 
 int bqq_decode_launches(const BqqDims* dims, int M) {

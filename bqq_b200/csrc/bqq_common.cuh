@@ -120,6 +120,19 @@ __device__ __forceinline__ float w_scale_from_bound(const float* bound_parts, fl
   return exp2f((float)s);
 }
 
+// One slot of a peer gather region: (data word, sequence number) as ONE scalar 64-bit access at
+// system scope.  A naturally aligned scalar 64-bit access is single-copy atomic; a two-element
+// vector access is not promised to be, so the pair never travels as .v2.u32.
+__device__ __forceinline__ void peer_slot_store(void* p, uint32_t data, uint32_t seq) {
+  const unsigned long long v = (unsigned long long)data | ((unsigned long long)seq << 32);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint2 peer_slot_load(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return make_uint2((uint32_t)v, (uint32_t)(v >> 32));
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? BQQ_OK : BQQ_ERR_CUDA;

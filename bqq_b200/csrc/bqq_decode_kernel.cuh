@@ -278,7 +278,7 @@ bqq_xprep_kernel(const XSource xs, int M, int cw, int Q, int cwp, int NB,
 
 // Final output of one lane (row `row` of X, local output column `o`) also travels to every rank of a
 // peer gather group: the 32-bit word that holds it goes with the gather's sequence number as one
-// 8-byte store into slot [row][rank-major column] of every region (see bqq_peer.cu).  16-bit outputs
+// scalar 64-bit store into slot [row][rank-major column] of every region (see bqq_peer.cu).  16-bit outputs
 // are paired with the neighbouring lane's (o is even on even lanes).  Every lane of the warp calls it.
 __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int row, int o, float v, int lane) {
   uint32_t word;
@@ -300,7 +300,7 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
   const size_t slot = ((size_t)row * p.peer_world + p.peer_rank) * p.peer_row_words + wcol;
   const size_t off = kPeerCtrlBytes + (count & 1u) * p.peer_half + slot * 8;
   for (int q = 0; q < p.peer_world; ++q)
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.peer_regions[q] + off), "r"(word), "r"(seq) : "memory");
+    peer_slot_store(p.peer_regions[q] + off, word, seq);
 }
 
 // MB: the CTA takes all bit layers of its row patch (4 warps each) instead of one.

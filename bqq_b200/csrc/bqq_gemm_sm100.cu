@@ -82,7 +82,6 @@ struct GemmParams {
   int a_sel[3];              // per pass: 0 = first activation map, 1 = second (low half of fp32 x)
   int b_row[3];              // per pass: row offset into the stacked W map (0 = hi / only part, N = lo part)
   uint32_t idesc;
-  volatile unsigned* dbg;    // optional host-mapped progress markers (NULL in normal use)
 };
 
 template <int BN>
@@ -123,9 +122,6 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const bool dbg_on = p.dbg && blockIdx.x == 0 && blockIdx.y == 0;
-#define BQQ_MARK(idx, val) do { if (dbg_on) { p.dbg[idx] = (val); __threadfence_system(); } } while (0)
-  if (threadIdx.x == 0) BQQ_MARK(1, tmem_base | 0x80000000u);   // setup + tensor-memory allocation done
 
   if (warp == 0) {
     if (lane == 0) {
@@ -140,7 +136,6 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
         const CUtensorMap* ma = p.a_sel[pass] == 0 ? &map_a0 : &map_a1;
         tma_load_2d(sA + s * kABytes, ma, full_bar + s, kb * kBK, m0);
         tma_load_2d(sB + s * kBBytes, &map_b, full_bar + s, kb * kBK, p.b_row[pass] + n0);
-        if (it == 0) BQQ_MARK(2, 1u);       // first copies issued
         issued = it + 1;
       }
       if (*failed) {
@@ -157,26 +152,21 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
         const int s = it % kStages;
         const uint32_t ph = (uint32_t)(it / kStages) & 1u;
         if (*failed || !mbar_wait(full_bar + s, ph)) { *failed = 1; ok = false; break; }
-        if (it == 0) BQQ_MARK(3, 1u);       // first stage landed
         tc_fence_after();
         const uint64_t adesc = make_smem_desc(smem_u32(sA + s * kABytes));
         const uint64_t bdesc = make_smem_desc(smem_u32(sB + s * kBBytes));
 #pragma unroll
         for (int k = 0; k < kBK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units per step
           tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc, (it | k) != 0 ? 1u : 0u);
-        if (it == 0) BQQ_MARK(4, 1u);       // first MMAs issued
         tc_commit(empty_bar + s);            // frees the stage when these MMAs have read it
-        if (it == 0) BQQ_MARK(5, 1u);       // first commit issued
       }
       tc_commit(acc_bar);                    // accumulator complete (or abandoned)
-      BQQ_MARK(6, 1u);
     }
   } else {
     // epilogue warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31
     const int quarter = warp & 3;
     const bool ok = mbar_wait(acc_bar, 0) && !*failed;
     if (!ok) *failed = 1;
-    if (warp == 2 && lane == 0) BQQ_MARK(7, ok ? 1u : 2u);   // accumulator barrier passed
     tc_fence_after();
     if (ok) {
       const float w_unscale = p.bound_parts ? 1.f / w_scale_from_bound(p.bound_parts, p.bound_mult) : 1.f;
@@ -187,7 +177,6 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
         uint32_t v[32];
         tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
         tc_wait_ld();
-        if (c == 0 && warp == 2 && lane == 0) BQQ_MARK(8, 1u);   // first tensor-memory load done
         const int nb = n0 + c * 32;
         if (m < p.M && nb < p.N) {
           const size_t row = (size_t)m * p.ldy;
@@ -234,10 +223,8 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
-    if (lane == 0) BQQ_MARK(9, 1u);
   }
   if (threadIdx.x == 0 && *failed) atomicExch(p.status, 1u);
-#undef BQQ_MARK
 }
 
 // ---- x staging: any dtype / stride -> dense 16-bit rows (hi, lo for fp32) ----
@@ -382,7 +369,6 @@ size_t prefill_workspace_bytes(const BqqDims* dims, int M) {
   return 256 + up256((size_t)2 * g.out_features() * K * 2) + 2 * up256((size_t)M * K * 2);
 }
 
-static volatile unsigned* g_gemm_dbg = nullptr;   // set only by the probe entry point below
 
 template <int BN>
 static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
@@ -472,7 +458,6 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   p.row_unscale = row_unscale;
   p.ldy = ldy; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
   p.M = M; p.N = N; p.K = K;
-  p.dbg = g_gemm_dbg;
   for (int i = 0; i < 3; ++i) { p.a_sel[i] = 0; p.b_row[i] = 0; }
   if (f16) {
     p.passes = 1;
@@ -491,7 +476,3 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
 }
 
 }  // namespace bqq
-
-// Probe hook (not part of the public header): progress markers of the GEMM kernel's first CTA
-// are written to `host_mapped` (device-visible pinned host memory, >= 16 words) when non-NULL.
-extern "C" void bqq_debug_set_gemm_markers(volatile unsigned* host_mapped) { bqq::g_gemm_dbg = host_mapped; }

@@ -12,6 +12,10 @@
 
 #include "bqq_common.cuh"
 
+// argument checks shared with bqq_forward_decode (bqq_api.cu)
+int bqq_decode_check_args(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
+                          int64_t ldy, const BqqFusion* fusion);
+
 namespace bqq {
 
 constexpr size_t kNoAllocBytes = BQQ_NOALLOC_SCRATCH_BYTES;
@@ -52,11 +56,9 @@ size_t bqq_noalloc_scratch_bytes(void) { return kNoAllocBytes; }
 
 int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                                int y_dtype, int64_t ldy, void* stream) {
-  if (!layer) return BQQ_ERR_NULL;
-  int rc = check_dims(&layer->dims);
+  // every argument check comes before anything is enqueued: a rejected call leaves the stream untouched
+  int rc = bqq_decode_check_args(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, nullptr);
   if (rc) return rc;
-  if (M <= 0) return BQQ_ERR_BAD_SHAPE;
-  if (M > BQQ_DECODE_MAX_M) return BQQ_ERR_UNSUPPORTED;
   const size_t need = decode_workspace_bytes(&layer->dims, M);
   if (need == 0) return BQQ_ERR_UNSUPPORTED;
   if (need > kNoAllocBytes) return BQQ_ERR_SCRATCH_LIMIT;      // layer / batch too large for the fixed array
@@ -64,13 +66,36 @@ int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype
   rc = scratch_address(&scratch);
   if (rc) return rc;
   // The array keeps whatever the previous call left.  The kernels overwrite everything they
-  // read except the completion counters, which must start at zero: clear them here.
-  if (cudaMemsetAsync(scratch, 0, decode_counter_bytes(), (cudaStream_t)stream) != cudaSuccess) {
+  // read except the completion counters, which must start at zero: clear them here.  The last
+  // counter word is the "a bounded wait gave up" status; it is left alone, so that it stays set
+  // until bqq_noalloc_status has reported it.
+  if (cudaMemsetAsync(scratch, 0, decode_counter_bytes() - 4, (cudaStream_t)stream) != cudaSuccess) {
     cudaGetLastError();
     return BQQ_ERR_CUDA;
   }
   // same argument checks and launch as the entry point with a caller workspace
   return bqq_forward_decode(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, scratch, kNoAllocBytes, stream);
+}
+
+// Synchronises `stream` and reports whether any call on the current device since the last report hit a
+// bounded device-side wait that gave up (BQQ_ERR_TIMEOUT: the outputs of those calls are invalid).
+// Reporting clears the word.  Like the entry point itself it allocates nothing.
+int bqq_noalloc_status(void* stream) {
+  void* scratch = nullptr;
+  int rc = scratch_address(&scratch);
+  if (rc) return rc;
+  unsigned st = 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  void* word = reinterpret_cast<char*>(scratch) + decode_counter_bytes() - 4;
+  if (cudaMemcpyAsync(&st, word, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+    cudaGetLastError();
+    return BQQ_ERR_CUDA;
+  }
+  if (st && (cudaMemsetAsync(word, 0, 4, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)) {
+    cudaGetLastError();
+    return BQQ_ERR_CUDA;
+  }
+  return st ? BQQ_ERR_TIMEOUT : BQQ_OK;
 }
 
 }  // extern "C"

@@ -5,15 +5,17 @@
 // all peers): control words and two halves of 8-byte slots, one slot per 32-bit word of the
 // gathered rows [rows][world*n].  A gather is one kernel per rank:
 //   send: every 32-bit word of my slice goes, together with the gather's sequence number, as one
-//         8-byte store into the matching slot of every rank's region (NVLink stores; an 8-byte
-//         store is indivisible, so no fence or separate flag is needed);
+//         scalar 64-bit store (st.relaxed.sys.b64) into the matching slot of every rank's region
+//         (NVLink stores; a naturally aligned scalar 64-bit access is single-copy atomic, so data and
+//         sequence number arrive together and no fence or separate flag is needed);
 //   receive: every slot of my own region is polled until it carries the sequence number, and its
 //         data word is written to the caller's tensor.
 // Consecutive gathers alternate between the two halves.  A rank can only start gather e+2 after it
 // has received gather e+1 from every peer, which the peers send after their gather e has returned,
 // so a half is never overwritten while its owner still reads it.
-// Every poll is bounded by a clock budget; when one gives up the kernel still finishes, the status
-// word is set and the next bqq_peer_status call reports BQQ_ERR_TIMEOUT.  The sequence number lives
+// Every poll is bounded by a clock budget (BqqPeerGroup::wait_cycles, about one second by default);
+// when one gives up the kernel still finishes, the status word is set and the next bqq_peer_status
+// call reports BQQ_ERR_TIMEOUT.  The sequence number lives
 // on the device, so a captured CUDA graph can replay the gather.
 #include <cuda_runtime.h>
 #include <string.h>
@@ -27,7 +29,7 @@ int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, i
 
 namespace bqq {
 
-constexpr long long kPeerWaitBudget = 2000000000LL;   // clock cycles (~1 s) before a poll gives up
+constexpr long long kPeerWaitBudget = 2000000000LL;   // default clock cycles (~1 s) before a poll gives up
 constexpr int kPeerThreads = 256;
 constexpr int kPeerMaxBlocks = 32;
 
@@ -40,15 +42,15 @@ struct PeerArgs {
   int row_words;                               // 32-bit words of one row of the local slice
   long long ld_src, ld_out;                    // row pitches in words
   unsigned long long half_bytes;               // bytes of one half of the slot area
+  long long wait_cycles;                       // clock budget of one poll
 };
 
+// slot = one scalar 64-bit word: data in the low half, sequence number in the high half
 __device__ __forceinline__ void st_slot(uint2* p, uint32_t data, uint32_t seq) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(seq) : "memory");
+  peer_slot_store(p, data, seq);
 }
 __device__ __forceinline__ uint2 ld_slot(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
+  return peer_slot_load(p);
 }
 
 __global__ void __launch_bounds__(kPeerThreads)
@@ -86,7 +88,7 @@ bqq_peer_gather_kernel(const PeerArgs a) {
     if (v.y != e) {
       const long long t0 = clock64();
       while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
-        if (clock64() - t0 > kPeerWaitBudget) { s_giveup = 1; break; }
+        if (clock64() - t0 > a.wait_cycles) { s_giveup = 1; break; }
         __nanosleep(32);
         v = ld_slot(slots + w);
       }
@@ -184,6 +186,7 @@ static int peer_gather_launch(const BqqPeerGroup* g, const void* y_local, int dt
   a.ld_src = (long long)((size_t)ldy * es / 4);
   a.ld_out = (long long)((size_t)ld_gathered * es / 4);
   a.half_bytes = peer_half_bytes(g->gather_bytes);
+  a.wait_cycles = g->wait_cycles ? (long long)g->wait_cycles : kPeerWaitBudget;
   const long long words = (long long)rows * a.row_words * g->world;
   int blocks = (int)((words + 2 * kPeerThreads - 1) / (2 * kPeerThreads));
   blocks = blocks < 1 ? 1 : (blocks > kPeerMaxBlocks ? kPeerMaxBlocks : blocks);

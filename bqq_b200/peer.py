@@ -24,10 +24,12 @@ class PeerGatherGroup:
     """Gather buffers of one process group.  `max_bytes` is the largest gathered result
     (rows * world * n_local * element size) the group will carry.
 
+    `wait_cycles` bounds every wait on a peer (GPU clock cycles; 0 = about one second).
+
     All ranks must create the group collectively and call gather() in the same order.  Gathers of one
     group are serialised by stream order on every rank; use one group per stream."""
 
-    def __init__(self, max_bytes: int, device: torch.device, group=None):
+    def __init__(self, max_bytes: int, device: torch.device, group=None, wait_cycles: int = 0):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -72,7 +74,7 @@ class PeerGatherGroup:
                 raise RuntimeError('bqq_b200: peer gather group could not be set up: '
                                    + '; '.join(f'rank {q}: {e}' for q, e in enumerate(errors) if e))
         self._desc = BqqPeerGroup(self.rank, self.world, (C.c_void_p * _cabi.MAX_PEERS)(*self._regions),
-                                  self.max_bytes)
+                                  self.max_bytes, int(wait_cycles))
 
     def descriptor(self):
         """ctypes reference to the BqqPeerGroup of this rank (for the C entry points)."""

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define BQQ_ABI_VERSION 1
+#define BQQ_ABI_VERSION 2
 
 /* error codes */
 #define BQQ_OK                0
@@ -210,6 +210,18 @@ int bqq_forward_decode_fused(const BqqLayer* layer, const void* x, int x_dtype, 
                              void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Status words of the workspaces (the reference has no counterpart: its kernels
+ * have no waits).  Both synchronise `stream` and return BQQ_ERR_TIMEOUT when a
+ * bounded device-side wait gave up in a call that used the workspace (its outputs
+ * are invalid), else BQQ_OK: bqq_decode_status reads the last counter word of a
+ * decode workspace (it stays set until the caller zero-fills the counters again),
+ * bqq_prefill_status the first word of a prefill workspace (cleared by every
+ * prefill call).
+ */
+int bqq_decode_status(const void* workspace, void* stream);
+int bqq_prefill_status(const void* workspace, void* stream);
+
+/*
  * Number of kernels one bqq_forward_decode call enqueues for this layer shape and
  * M (1 or 2: short single-chunk layers at M = 1 prepare x inside the decode
  * kernel, all others launch a preparation kernel first); negative BQQ_ERR_* for
@@ -253,10 +265,16 @@ int bqq_forward_host(const BqqLayer* layer, const void* x_host, int x_dtype, int
  * outside any stream capture.  All calls share the one array and it keeps the
  * previous call's contents (the call clears the counters it relies on): calls
  * that overlap on the GPU, on any streams, race with each other.
+ * The array's last counter word is the decode kernel's "a bounded wait gave up"
+ * status; the call does not clear it.  bqq_noalloc_status synchronises `stream`,
+ * returns BQQ_ERR_TIMEOUT if any call on the current device since the previous
+ * report set it (their outputs are invalid) and clears it; it allocates nothing
+ * either.  Arguments are checked before anything is enqueued.
  */
 size_t bqq_noalloc_scratch_bytes(void);
 int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
                                void* y, int y_dtype, int64_t ldy, void* stream);
+int bqq_noalloc_status(void* stream);
 
 /*
  * Column gather for row-patch sharded layers by peer-to-peer stores (one process
@@ -278,7 +296,7 @@ int bqq_forward_decode_noalloc(const BqqLayer* layer, const void* x, int x_dtype
  * Slices travel as 32-bit words: n_local, ldy and ld_gathered times the element
  * size must be multiples of 4 bytes (BQQ_ERR_MISALIGNED otherwise).
  * Every rank must issue the same sequence of gathers on the same group.  Waits on
- * peers are bounded (about one second); if one gives up the kernel still ends and
+ * peers are bounded (BqqPeerGroup.wait_cycles, about one second by default); if one gives up the kernel still ends and
  * bqq_peer_status (which synchronises `stream`) returns BQQ_ERR_TIMEOUT.  No
  * reduction is involved, so the gathered rows equal the single-GPU output bit for
  * bit.  The call can be captured in a CUDA graph.
@@ -289,6 +307,8 @@ typedef struct BqqPeerGroup {
   int32_t rank, world;
   void* regions[BQQ_MAX_PEERS];   /* every rank's region as mapped in this process */
   uint64_t gather_bytes;          /* largest gathered result, as given to bqq_peer_alloc */
+  uint64_t wait_cycles;           /* clock cycles a wait on a peer may take before it gives up;
+                                     0 = the default (2e9, about one second) */
 } BqqPeerGroup;
 
 size_t bqq_peer_region_bytes(size_t gather_bytes);

@@ -27,7 +27,7 @@ def test_exports_match_header(cabi):
     for name in declared:
         assert hasattr(cabi.lib, name), f'{name} declared in the header but not exported'
     assert declared == set(cabi.EXPORTS)
-    assert cabi.lib.bqq_abi_version() == 1
+    assert cabi.lib.bqq_abi_version() == 2
 
 
 def test_strerror_and_codes(cabi):

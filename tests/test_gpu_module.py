@@ -103,7 +103,7 @@ def test_errors():
         with pytest.raises(RuntimeError, match='last dim'):
             bq(torch.randn(1, 65).cuda())
         with pytest.raises(RuntimeError, match='unsupported activation dtype'):
-            bq(X.double().cuda())
+            bq(X.long().cuda())
 
 
 def test_sharded_rows_equal_unsharded():
@@ -213,3 +213,63 @@ def test_plane_layer_from_patches_equals_dense_route():
     again = torch.load(buf, weights_only=False)
     X = torch.randn(2, 6 * 32, generator=g).cuda()
     assert torch.equal(_fwd(again, X), _fwd(dense, X))
+
+
+def test_reference_made_pickles_run_on_the_gpu():
+    """Whole-module pickles written by the reference's own builder and classes
+    (tests/golden/make_pickles.py: replace_linear_with_bqq + torch.save, pack_existing_model) load onto
+    this package's classes and reproduce the reference's stored fp32 outputs."""
+    import os
+
+    import bqq_b200
+    from tests.helpers import GOLDEN
+    bqq_b200.install()
+    io = np.load(os.path.join(GOLDEN, 'ref_model_io.npz'))
+    X = torch.from_numpy(io['X'])
+    for fname, cls in (('ref_model_bq.pth', bqq_b200.BinaryQuadratic),
+                       ('ref_model_bq-packed.pth', bqq_b200.PackedBinaryQuadratic)):
+        model = torch.load(os.path.join(GOLDEN, fname), weights_only=False)
+        assert type(model.fc1) is cls and type(model.fc2) is cls
+        model = model.cuda()
+        y = _fwd(model, X.cuda())
+        assert O.max_rel_err(y.cpu().numpy(), io['y_ref_fp32']) < 1e-4, fname
+        W = model.fc1.get_weight(torch.float32)
+        assert np.abs(W.cpu().numpy() - io['fc1_weight']).max() < 1e-6
+
+
+@pytest.mark.parametrize('geom,lead', [((2, 4, 4, 32, 32, 32), (1,)), ((2, 2, 2, 32, 32, 12), (3,)),
+                                       ((3, 2, 8, 32, 32, 16), (2, 20))])
+def test_extension_call_signature(geom, lead):
+    """bqq_cuda_ext._get_ext().bqq_forward(Y_packed, Z_packed, X, a, b, c, d, bias): the call the
+    reference's packed layer makes (src/bqq_modules.py:217-230; src/bqq_cuda.cu:289-297)."""
+    from bqq_b200 import bqq_cuda_ext
+    from bqq_b200.bqq_modules import BinaryQuadratic, PackedBinaryQuadratic
+    Y, Z, A, bias, _ = synth_layer(*geom, 1, seed=21, bias=True)
+    pk = PackedBinaryQuadratic.from_unpacked(BinaryQuadratic(Y.float(), Z.float(), A, bias=bias)).cuda()
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(*lead, geom[2] * geom[4], generator=g)
+    ext = bqq_cuda_ext._get_ext()
+    y = ext.bqq_forward(pk.Y_packed, pk.Z_packed, X.cuda(), pk.a, pk.b, pk.c, pk.d, pk.bias)
+    assert tuple(y.shape) == (*lead, geom[1] * geom[3]) and y.dtype == torch.float32
+    ref = oracle_forward_t(Y, Z, A, bias, X.reshape(-1, X.shape[-1])).reshape(y.shape)
+    tol = 1e-4 if X.numel() // X.shape[-1] <= 16 else 1e-3
+    assert O.max_rel_err(y.cpu().numpy(), ref) < tol
+    # "no bias" is an empty tensor in the reference's call; coefficients are read on every call
+    y0 = bqq_cuda_ext.bqq_forward(pk.Y_packed, pk.Z_packed, X.cuda(), pk.a, pk.b, pk.c, pk.d,
+                                  torch.empty(0, device='cuda'))
+    ref0 = oracle_forward_t(Y, Z, A, None, X.reshape(-1, X.shape[-1])).reshape(y.shape)
+    assert O.max_rel_err(y0.cpu().numpy(), ref0) < tol
+    y2 = ext.bqq_forward(pk.Y_packed, pk.Z_packed, X.cuda(), pk.a * 2, pk.b * 2, pk.c * 2, pk.d * 2, None)
+    assert O.max_rel_err(y2.cpu().numpy(), 2 * ref0) < tol
+    assert len(ext._engines) >= 1
+
+
+def test_fp64_activations_go_through_fp32():
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, _, X = synth_layer(2, 4, 4, 32, 32, 32, 3, seed=13)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A).cuda()
+    y = _fwd(bq, X.double().cuda())
+    assert y.dtype == torch.float64
+    assert O.max_rel_err(y.cpu().numpy(), oracle_forward_t(Y, Z, A, None, X)) < 1e-4
+    with pytest.raises(RuntimeError, match='floating point'):
+        _fwd(bq, torch.zeros(1, 128, dtype=torch.int32, device='cuda'))

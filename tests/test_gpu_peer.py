@@ -1,6 +1,7 @@
 """GPU: the peer-to-peer column gather (bqq_peer_gather).  A one-rank group runs the whole protocol
-(own flags and acknowledgements) on a single GPU; with two or more GPUs a two-process run checks the
-gathered values against every rank's slice, repeated gathers, and CUDA-graph replay."""
+(own slots) on a single GPU; with two or more GPUs a two-process run checks the gathered values against
+every rank's slice, repeated gathers, and CUDA-graph replay.  The time-out path is exercised in one
+process against a region that nobody writes."""
 import os
 import socket
 
@@ -113,3 +114,45 @@ def test_peer_gather_single_rank(tmp_path):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
 def test_peer_gather_two_ranks(tmp_path):
     _run(2, tmp_path)
+
+
+def test_wait_on_a_silent_peer_runs_out_and_is_reported():
+    """Failure detection without a fault: a two-rank group whose second region is a local buffer that no
+    rank ever writes.  The gather's polls on that rank's slots run out after the group's clock budget
+    (a few milliseconds here), the kernel ends normally, bqq_peer_status reports BQQ_ERR_TIMEOUT, and a
+    fresh group on the same GPU works afterwards."""
+    import ctypes as C
+
+    from bqq_b200 import _cabi
+    lib = _cabi.lib
+    dev = torch.device('cuda', 0)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    gather_bytes = 2 * 256 * 4
+    regions = []
+    for _ in range(2):
+        ptr, handle = C.c_void_p(), C.create_string_buffer(_cabi.PEER_HANDLE_BYTES)
+        _cabi.check(lib.bqq_peer_alloc(gather_bytes, C.byref(ptr), handle), 'bqq_peer_alloc')
+        regions.append(ptr.value)
+    try:
+        silent = _cabi.BqqPeerGroup(0, 2, (C.c_void_p * _cabi.MAX_PEERS)(*regions), gather_bytes, 5_000_000)
+        y = torch.arange(256, dtype=torch.float32, device=dev).reshape(1, 256)
+        out = torch.full((1, 512), -1.0, device=dev)
+        _cabi.check(lib.bqq_peer_gather(C.byref(silent), y.data_ptr(), _cabi.F32, 1, 256, 256, out.data_ptr(), 512, stream),
+                    'bqq_peer_gather')
+        torch.cuda.synchronize()                                  # the kernel returns by itself
+        assert lib.bqq_peer_status(C.byref(silent), stream) == -8     # BQQ_ERR_TIMEOUT
+        assert _cabi.strerror(-8) == 'a bounded device-side wait gave up'
+        assert torch.equal(out[:, :256], y)                       # the own slice still arrived
+        # the context is intact: a one-rank group on a fresh region gathers correctly, twice
+        alone = _cabi.BqqPeerGroup(0, 1, (C.c_void_p * _cabi.MAX_PEERS)(regions[1]), gather_bytes, 0)
+        for rep in range(2):
+            out1 = torch.empty(1, 256, device=dev)
+            _cabi.check(lib.bqq_peer_gather(C.byref(alone), (y + rep).data_ptr(), _cabi.F32, 1, 256, 256, out1.data_ptr(),
+                                            256, stream), 'bqq_peer_gather')
+            assert lib.bqq_peer_status(C.byref(alone), stream) == 0
+            assert torch.equal(out1, y + rep)
+    finally:
+        torch.cuda.synchronize()
+        for p in regions:
+            lib.bqq_peer_free(p)

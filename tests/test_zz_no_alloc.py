@@ -51,6 +51,8 @@ def test_noalloc_matches_workspace_entry_point_twice():
         # same kernels, same reduction order: identical up to the tolerance the other decode tests use
         assert (y_new.float() - y_ref.float()).abs().max().item() <= 1e-4 * scale
         assert torch.equal(y_new, y_ref)
+    # no bounded wait gave up in either call; the report synchronises the stream
+    assert lib.bqq_noalloc_status(torch.cuda.current_stream().cuda_stream) == 0
 
 
 def test_noalloc_rejects_oversized_request():
@@ -63,3 +65,8 @@ def test_noalloc_rejects_oversized_request():
     layer = _cabi.BqqLayer(big, p, p, p, p, p, p, None, 0, 0)
     rc = lib.bqq_forward_decode_noalloc(layer, p, _cabi.BF16, 16, 448 * 32, p, _cabi.BF16, 1024 * 32, None)
     assert rc == -10 and 'scratch' in _cabi.strerror(rc)
+    # a bad argument is refused before anything is enqueued (here: a NULL activation pointer)
+    small = _cabi.dims(2, 4, 4, 32, 32, 32)
+    layer = _cabi.BqqLayer(small, p, p, p, p, p, p, None, 0, 0)
+    assert lib.bqq_forward_decode_noalloc(layer, None, _cabi.BF16, 1, 128, p, _cabi.BF16, 128, None) == -1
+    assert lib.bqq_noalloc_status(None) == 0
