@@ -21,8 +21,10 @@ constexpr int kGroup = 4;  // col patches interleaved in one 128-bit lane load
 //   Z [rw][NS][RT][QT][32 lanes][4 sub]     Y [rw][NS][PT][RT][32 lanes][4 sub]
 // Lane = 4*g + t.  Bits inside a word (fragment order of the int8 tensor-core
 // operand the decode kernel expands with byte masks):
-//   Z bit 8e + 4qh + rr = Z[k = 32rt + g + 8rr][q = 32qt + 16qh + 4t + e]
+//   Z bit 8e + 4qh + rr = Z[k = 32rt + 4g + rr][q = 32qt + 16qh + 4t + e]
 //   Y bit 8e + 4kh + rr = Y[p = 32pt + g + 8rr][k = 32rt + 16kh + 4t + e]
+// (the four rows of a Z word are four consecutive ranks: the lane that finishes them in the decode kernel
+// owns exactly one B-operand word of the second contraction, whose k order is that of the Y word's bytes)
 struct Geom {
   int bw, rw, cw, P, Q, r;
   int PT, QT, RT;      // 32-blocks of P, Q, r
@@ -43,7 +45,7 @@ struct Geom {
 
   // word offset and bit position of Z[b,i,j][k][q]
   __host__ __device__ size_t z_word(int b, int i, int j, int k, int q, int* bit) const {
-    const int rt = k >> 5, rr = (k >> 3) & 3, g = k & 7;
+    const int rt = k >> 5, g = (k >> 2) & 7, rr = k & 3;
     const int qt = q >> 5, qh = (q >> 4) & 1, t = (q >> 2) & 3, e = q & 3;
     *bit = 8 * e + 4 * qh + rr;
     const size_t s = (size_t)b * JG + j / kGroup;

@@ -20,6 +20,15 @@
 // separate B-operand columns, so the integer products are exact and the only
 // errors are the two roundings (about 2^-16 of the patch maximum of |x|).
 //
+// How the two contractions meet (M = 1): the four col patches of a super-group put their x
+// digits into four different column pairs of the first contraction's B operand (the other
+// columns are zero) and accumulate into ONE accumulator tile, so lane (g,t) ends up with the
+// sums of col patch t for the four ranks 4g .. 4g+3 of every 32-rank block - no selection
+// between registers.  It turns them into digits, transposes the 4 x 3 bytes in registers and
+// stores one word per digit; a lane of the second contraction reads the words of all four col
+// patches with two 128-bit loads.  With several rows of X the column pairs carry the rows
+// instead and the col patches are handled one after the other.
+//
 // Work split: CTA = (row patch i, bit layer b, chunk of col-patch groups, M tile);
 // warp w owns a contiguous run of super-groups of the chunk and streams its plane
 // words and x digits through a private ring of shared-memory slots filled by 16-byte
@@ -125,6 +134,10 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int sub) {
 }
 
 constexpr int kMaxSgw = 32;              // upper bound of super-groups per warp (resident coefficients: 64 B each)
+// u digit exchange at M = 1, per 32-rank block: 128 words [digit d][lane group G' = G ^ 4 (d & 1)][sub], G = 0..7 the
+// lane group g that produced the word (ranks 4G .. 4G+3).  Producers (fixed d, all G and sub) and consumers (128-bit
+// loads over sub for G in 0..3 or 4..7 and two neighbouring digits) both touch every bank once.
+constexpr int kUBlock = 128;
 
 // Shared-memory carve-up (bytes), shared by host plan and kernel.  Per warp a ring of `stages`
 // slots, each holding one super-group: its Z words, Y words and the x digits of the CTA's rows.
@@ -145,7 +158,9 @@ struct DecodeSmem {
     ring = o;  o += nwarps * stages * slot;
     coef = o;  o += bpc * 4 * nsg * 16;               // float [bit][a|b|c|d][nsg*4]
     meta = o;  o += bpc * NB * 3 * nsg * 16;          // float [bit][NB][scale|sum|l1][nsg*4]
-    udig = o;  o += nwarps * kGroup * NB * (4 * RT * 32 + (NB == 1 ? 0 : 16));  // u8 [warps][4 sub][NB][4 slots][RP] (+ pad)
+    // u digits: M = 1: words [warps][RT][4 digits][8 lane groups][4 sub];
+    // more rows: bytes [warps][4 sub][NB][4 digits][RP] (+ 16 bytes of padding per row of X)
+    udig = o;  o += nwarps * (NB == 1 ? RT * kUBlock * 4 : kGroup * NB * (4 * RT * 32 + 16));
     red = o;   o += nwarps * NB * PT * 32 * 4;        // f32 [warps][NB][PP]
     // CTAs that take all bit layers prepare x themselves: digits and statistics of the whole chunk
     xres = o;  o += bpc > 1 ? nsg * NB * 2 * QT * 128 : 0;   // uint4 [nsg][NB][digit][QT][8]
@@ -441,18 +456,23 @@ bqq_decode_kernel(const DecodeParams p) {
     cp_async_commit();
   }
 
-  // ---- digit exchange buffer: slots 0..2 are rewritten for every col patch, slot 3 is a column of
-  // ones whose products count the Y bits of each row (removes the offset of the unsigned digits)
-  // [sub][row of X][slot][rank]; rows of X are 16 bytes further apart than their 4 slots need, so that the
-  // byte stores of lanes with different t (different rows of X) and the word loads of the two rows an
-  // n-tile covers fall into different banks
-  constexpr int kURow = 4 * RP + (NB == 1 ? 0 : 16);
+  // ---- digit exchange buffer: digits 0..2 are rewritten for every super-group (col patch), digit 3 is a
+  // column of ones whose products count the Y bits of each row (removes the offset of the unsigned digits)
+  // M > 1: bytes [sub][row of X][digit][rank]; rows of X are 16 bytes further apart than their 4 digits need, so
+  // that the word loads of the two rows an n-tile covers fall into different banks
+  constexpr int kURow = 4 * RP + 16;
   constexpr int kUSub = NB * kURow;                  // bytes of one col patch's u digits
-  uint8_t* my_udig = sm + L.udig + (size_t)warp * kGroup * kUSub;
-  // only the ones need writing: slots 0..2 are fully rewritten before every use
-  for (int e = lane; e < kGroup * NB * (RP / 4); e += 32) {
-    const int sub = e / (NB * (RP / 4)), rem = e % (NB * (RP / 4));
-    reinterpret_cast<uint32_t*>(my_udig + sub * kUSub + (rem / (RP / 4)) * kURow + 3 * RP)[rem % (RP / 4)] = 0x01010101u;
+  uint8_t* my_udig = sm + L.udig + (size_t)warp * (NB == 1 ? RT * kUBlock * 4 : kGroup * kUSub);
+  // only the ones need writing: digits 0..2 are fully rewritten before every use
+  if (NB == 1) {
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+      reinterpret_cast<uint32_t*>(my_udig)[rt * kUBlock + 96 + lane] = 0x01010101u;
+  } else {
+    for (int e = lane; e < kGroup * NB * (RP / 4); e += 32) {
+      const int sub = e / (NB * (RP / 4)), rem = e % (NB * (RP / 4));
+      reinterpret_cast<uint32_t*>(my_udig + sub * kUSub + (rem / (RP / 4)) * kURow + 3 * RP)[rem % (RP / 4)] = 0x01010101u;
+    }
   }
   bool ok = mbar_wait(bar, 0);
 
@@ -539,20 +559,24 @@ bqq_decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[pt][mt][nt][e] = 0;
   float cacc = 0.f;
-  const float rs_t = 1.f / (float)(1 << t);
-  const bool t_odd = (t & 1) != 0, t_hi = (t & 2) != 0;   // lane (g,t) finishes rank g + 8t
-  // lane constants: where this lane's B-operand column (n = g) finds its x digits inside a slot, where
-  // the lane's row of X keeps scale and sum, where its u digits go and come from
-  const int xlane = kXoff + (NB == 1 ? (g & 1) : g) * (QT * 8) + t;
+  // lane constants.  M = 1: column n = g of the first contraction's B operand carries digit g & 1 of col patch
+  // g >> 1 (zero for the other col patches); the lane finishes col patch t.  M > 1: column pair t carries row t of
+  // X; the lane finishes that row for every col patch.
+  const int my_sub = g >> 1;
+  const int xword = NB == 1 ? kXoff * 4 + (g & 1) * (QT * 32) + t * 4 + my_sub : 0;   // 32-bit words inside a slot
+  const int xlane = kXoff + g * (QT * 8) + t;                                          // uint4 index (M > 1)
   const float* mrow = smeta + my_beta * 3 * nsg * 4;   // [alpha | beta | gamma] of this lane's row of X
-  uint8_t* ust = my_udig + (NB == 1 ? g + 8 * t : t * kURow + g);
+  // where the lane's u digits go ...
+  uint8_t* ust = NB == 1 ? my_udig + 4 * lane : my_udig + t * kURow + 4 * g;   // M = 1: word 4G + sub of digit 0
+  // ... and where its B operand of the second contraction comes from
   const uint8_t* uld[NT2];
 #pragma unroll
   for (int nt = 0; nt < NT2; ++nt) {
-    const int beta = NB == 1 ? 0 : 2 * nt + (g >> 2);
-    const int slot = NB == 1 ? min(g, 3) : (g & 3);      // slot 3: the column of ones
-    uld[nt] = my_udig + beta * kURow + slot * RP + 4 * t;
+    const int beta = 2 * nt + (g >> 2);                  // M > 1: row of X and digit of column n = g
+    uld[nt] = NB == 1 ? my_udig + 4 * (32 * (g & 3) + 4 * t) : my_udig + beta * kURow + (g & 3) * RP + 4 * t;
   }
+  // M = 1: the words of lane groups t (ranks 4t ..: first half of k) and t + 4 (second half) of digit g & 3
+  const int ulo = (g & 1) ? 64 : 0, uhi = 64 - ulo;      // byte offsets from uld[0]
 #pragma unroll(NB == 1 ? 4 : 1)
   for (int n = 0; n < nw; ++n) {
     // refill the slot consumed in the previous iteration with the super-group S - 1 ahead
@@ -578,99 +602,159 @@ bqq_decode_kernel(const DecodeParams p) {
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt)
         yw[pt][rt] = (pt < PTg && rt < RTg) ? ys[(pt * RTg + rt) * 32 + lane] : make_uint4(0u, 0u, 0u, 0u);
-    // per super-group: folded coefficients and the x digit registers of its 4 col patches
-    const float4 va = *reinterpret_cast<const float4*>(mrow + li * 4);
-    const float4 vb = *reinterpret_cast<const float4*>(mrow + nsg * 4 + li * 4);
-    const float4 vc = *reinterpret_cast<const float4*>(mrow + nsg * 8 + li * 4);
-    const float ca4[4] = {va.x, va.y, va.z, va.w};
-    const float cb4[4] = {vb.x, vb.y, vb.z, vb.w};
-    const float cc4[4] = {vc.x, vc.y, vc.z, vc.w};
-    uint32_t bx0[kGroup][QT], bx1[kGroup][QT];
+    if (NB == 1) {
+      // ---- M = 1 --------------------------------------------------------------------------------------
+      // x digits of this lane's B column: digit g & 1 of col patch g >> 1 (one word per half of q)
+      const uint32_t* xw = reinterpret_cast<const uint32_t*>(MB ? xres + li * xq - kXoff : zs) + xword;
+      uint32_t bx0[QT], bx1[QT];
 #pragma unroll
-    for (int qt = 0; qt < QT; ++qt) {
-      const uint4* xd = MB ? xres + li * xq - kXoff : zs;   // MB: digits of the whole chunk are resident
-      const uint4 h0 = xd[xlane + qt * 8];
-      const uint4 h1 = xd[xlane + qt * 8 + 4];
-      bx0[0][qt] = h0.x; bx0[1][qt] = h0.y; bx0[2][qt] = h0.z; bx0[3][qt] = h0.w;
-      bx1[0][qt] = h1.x; bx1[1][qt] = h1.y; bx1[2][qt] = h1.z; bx1[3][qt] = h1.w;
-    }
-
-#pragma unroll
-    for (int sub = 0; sub < kGroup; ++sub) {
-      const float ca = ca4[sub], cb = cb4[sub], cc = cc4[sub];
-
-      // ---- first contraction: T[k][digit] = sum_q Z[k][q] xdigit[q] --------------------
+      for (int qt = 0; qt < QT; ++qt) {
+        bx0[qt] = xw[qt * 32];
+        bx1[qt] = xw[qt * 32 + 16];
+      }
+      // folded coefficients of col patch t
+      const float ca = mrow[li * 4 + t], cb = mrow[nsg * 4 + li * 4 + t], cc = mrow[nsg * 8 + li * 4 + t];
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt) {
+        // first contraction, all four col patches into one tile: T[k][2 sub + digit] = sum_q Z_sub[k][q] xdigit_sub[q]
         int c1[2][4];
 #pragma unroll
-        for (int qt = 0; qt < QT; ++qt) {
-          const uint32_t w = pick(zw[rt][qt], sub);
-          const uint32_t w4 = w >> 4;
-          if (qt == 0) {
-            mma_u8s8_first(c1[0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
-                           bx0[sub][qt], bx1[sub][qt]);
-            mma_u8s8_first(c1[1], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
-                           bx0[sub][qt], bx1[sub][qt]);
-          } else {
-            mma_u8s8(c1[0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
-                     bx0[sub][qt], bx1[sub][qt]);
-            mma_u8s8(c1[1], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
-                     bx0[sub][qt], bx1[sub][qt]);
+        for (int sub = 0; sub < kGroup; ++sub) {
+#pragma unroll
+          for (int qt = 0; qt < QT; ++qt) {
+            const uint32_t w = pick(zw[rt][qt], sub);
+            const uint32_t w4 = w >> 4;
+            const uint32_t b0 = my_sub == sub ? bx0[qt] : 0u, b1 = my_sub == sub ? bx1[qt] : 0u;
+            if (sub == 0 && qt == 0) {
+              mma_u8s8_first(c1[0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u, b0, b1);
+              mma_u8s8_first(c1[1], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u, b0, b1);
+            } else {
+              mma_u8s8(c1[0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u, b0, b1);
+              mma_u8s8(c1[1], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u, b0, b1);
+            }
           }
         }
-        if (NB == 1) {
-          // every lane sees (lo, hi) in its two columns for ranks g, g+8 (c1[0]) and g+16, g+24 (c1[1]);
-          // lane (g,t) finishes rank k = 32rt + g + 8t
-          const int lo = t_hi ? (t_odd ? c1[1][2] : c1[1][0]) : (t_odd ? c1[0][2] : c1[0][0]);
-          const int hi = t_hi ? (t_odd ? c1[1][3] : c1[1][1]) : (t_odd ? c1[0][3] : c1[0][1]);
-          const float tf = (float)(lo + (hi << 8)) * rs_t;
+        // the lane's columns 2t, 2t+1 are (lo, hi) of col patch t; its rows are the ranks 32rt + 4g + rr
+        uint32_t D[4];
+#pragma unroll
+        for (int rr = 0; rr < 4; ++rr) {
+          const int lo = c1[rr >> 1][2 * (rr & 1)];
+          const int hi = c1[rr >> 1][2 * (rr & 1) + 1];
+          const float tf = (float)(lo + (hi << 8)) * (1.f / (float)(1 << rr));
           cacc = fmaf(cc, tf, cacc);
-          const uint32_t D = (uint32_t)__float_as_int(fmaf(ca, tf, cb));
-          uint8_t* dst = ust + sub * kUSub + rt * 32;
-          dst[0] = (uint8_t)D;
-          dst[RP] = (uint8_t)(D >> 8);
-          dst[2 * RP] = (uint8_t)(D >> 16);
-        } else {
-          // lane (g,t) owns row t of X: finishes ranks k = 32rt + g + 8rr, rr = 0..3
+          D[rr] = (uint32_t)__float_as_int(fmaf(ca, tf, cb));
+        }
+        // 4 ranks x 3 digits -> one word per digit (byte e = rank 4g + e): the B operand words of the second contraction
+        const uint32_t p01a = __byte_perm(D[0], D[1], 0x5140), p01b = __byte_perm(D[0], D[1], 0x6262);
+        const uint32_t p23a = __byte_perm(D[2], D[3], 0x5140), p23b = __byte_perm(D[2], D[3], 0x6262);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(ust) + rt * kUBlock;
+        dst[0] = __byte_perm(p01a, p23a, 0x5410);
+        dst[32 + (lane ^ 16) - lane] = __byte_perm(p01a, p23a, 0x7632);
+        dst[64] = __byte_perm(p01b, p23b, 0x5410);
+      }
+      __syncwarp();
+
+      // ---- second contraction: V[p][digit] += sum_k Y[p][k] udigit[k] --------------------
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        const uint4 bu0 = *reinterpret_cast<const uint4*>(uld[0] + rt * 4 * kUBlock + ulo);
+        const uint4 bu1 = *reinterpret_cast<const uint4*>(uld[0] + rt * 4 * kUBlock + uhi);
+#pragma unroll
+        for (int sub = 0; sub < kGroup; ++sub) {
+#pragma unroll
+          for (int pt = 0; pt < PT; ++pt) {
+            const uint32_t w = pick(yw[pt][rt], sub);
+            const uint32_t w4 = w >> 4;
+            mma_u8u8(acc[pt][0][0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
+                     pick(bu0, sub), pick(bu1, sub));
+            mma_u8u8(acc[pt][1][0], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
+                     pick(bu0, sub), pick(bu1, sub));
+          }
+        }
+      }
+    } else {
+      // ---- several rows of X: column pair t of the first contraction carries row t ---------------------
+      // per super-group: folded coefficients and the x digit registers of its 4 col patches
+      const float4 va = *reinterpret_cast<const float4*>(mrow + li * 4);
+      const float4 vb = *reinterpret_cast<const float4*>(mrow + nsg * 4 + li * 4);
+      const float4 vc = *reinterpret_cast<const float4*>(mrow + nsg * 8 + li * 4);
+      const float ca4[4] = {va.x, va.y, va.z, va.w};
+      const float cb4[4] = {vb.x, vb.y, vb.z, vb.w};
+      const float cc4[4] = {vc.x, vc.y, vc.z, vc.w};
+      uint32_t bx0[kGroup][QT], bx1[kGroup][QT];
+#pragma unroll
+      for (int qt = 0; qt < QT; ++qt) {
+        const uint4 h0 = zs[xlane + qt * 8];
+        const uint4 h1 = zs[xlane + qt * 8 + 4];
+        bx0[0][qt] = h0.x; bx0[1][qt] = h0.y; bx0[2][qt] = h0.z; bx0[3][qt] = h0.w;
+        bx1[0][qt] = h1.x; bx1[1][qt] = h1.y; bx1[2][qt] = h1.z; bx1[3][qt] = h1.w;
+      }
+#pragma unroll
+      for (int sub = 0; sub < kGroup; ++sub) {
+        const float ca = ca4[sub], cb = cb4[sub], cc = cc4[sub];
+        // ---- first contraction: T[k][2 row + digit] = sum_q Z[k][q] xdigit_row[q] --------------------
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+          int c1[2][4];
+#pragma unroll
+          for (int qt = 0; qt < QT; ++qt) {
+            const uint32_t w = pick(zw[rt][qt], sub);
+            const uint32_t w4 = w >> 4;
+            if (qt == 0) {
+              mma_u8s8_first(c1[0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
+                             bx0[sub][qt], bx1[sub][qt]);
+              mma_u8s8_first(c1[1], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
+                             bx0[sub][qt], bx1[sub][qt]);
+            } else {
+              mma_u8s8(c1[0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
+                       bx0[sub][qt], bx1[sub][qt]);
+              mma_u8s8(c1[1], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
+                       bx0[sub][qt], bx1[sub][qt]);
+            }
+          }
+          // lane (g,t) owns row t of X: finishes the ranks k = 32rt + 4g + rr, rr = 0..3
+          uint32_t D[4];
 #pragma unroll
           for (int rr = 0; rr < 4; ++rr) {
             const int lo = c1[rr >> 1][2 * (rr & 1)];
             const int hi = c1[rr >> 1][2 * (rr & 1) + 1];
             const float tf = (float)(lo + (hi << 8)) * (1.f / (float)(1 << rr));
             cacc = fmaf(cc, tf, cacc);
-            const uint32_t D = (uint32_t)__float_as_int(fmaf(ca, tf, cb));
-            uint8_t* dst = ust + sub * kUSub + rt * 32 + 8 * rr;
-            dst[0] = (uint8_t)D;
-            dst[RP] = (uint8_t)(D >> 8);
-            dst[2 * RP] = (uint8_t)(D >> 16);
+            D[rr] = (uint32_t)__float_as_int(fmaf(ca, tf, cb));
           }
+          // the four ranks are neighbours in the digit rows: one word per digit
+          const uint32_t p01a = __byte_perm(D[0], D[1], 0x5140), p01b = __byte_perm(D[0], D[1], 0x6262);
+          const uint32_t p23a = __byte_perm(D[2], D[3], 0x5140), p23b = __byte_perm(D[2], D[3], 0x6262);
+          uint32_t* dst = reinterpret_cast<uint32_t*>(ust + sub * kUSub + rt * 32);
+          dst[0] = __byte_perm(p01a, p23a, 0x5410);
+          dst[RP / 4] = __byte_perm(p01a, p23a, 0x7632);
+          dst[2 * RP / 4] = __byte_perm(p01b, p23b, 0x5410);
         }
       }
-    }
-    __syncwarp();
+      __syncwarp();
 
-    // ---- second contraction: V[p][digit] += sum_k Y[p][k] udigit[k] --------------------
+      // ---- second contraction: V[p][2 row' + digit'] += sum_k Y[p][k] udigit[k] --------------------
 #pragma unroll
-    for (int sub = 0; sub < kGroup; ++sub) {
+      for (int sub = 0; sub < kGroup; ++sub) {
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-        uint32_t bu[NT2][2];
-#pragma unroll
-        for (int nt = 0; nt < NT2; ++nt) {
-          bu[nt][0] = *reinterpret_cast<const uint32_t*>(uld[nt] + sub * kUSub + rt * 32);
-          bu[nt][1] = *reinterpret_cast<const uint32_t*>(uld[nt] + sub * kUSub + rt * 32 + 16);
-        }
-#pragma unroll
-        for (int pt = 0; pt < PT; ++pt) {
-          const uint32_t w = pick(yw[pt][rt], sub);
-          const uint32_t w4 = w >> 4;
+        for (int rt = 0; rt < RT; ++rt) {
+          uint32_t bu[NT2][2];
 #pragma unroll
           for (int nt = 0; nt < NT2; ++nt) {
-            mma_u8u8(acc[pt][0][nt], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
-                     bu[nt][0], bu[nt][1]);
-            mma_u8u8(acc[pt][1][nt], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
-                     bu[nt][0], bu[nt][1]);
+            bu[nt][0] = *reinterpret_cast<const uint32_t*>(uld[nt] + sub * kUSub + rt * 32);
+            bu[nt][1] = *reinterpret_cast<const uint32_t*>(uld[nt] + sub * kUSub + rt * 32 + 16);
+          }
+#pragma unroll
+          for (int pt = 0; pt < PT; ++pt) {
+            const uint32_t w = pick(yw[pt][rt], sub);
+            const uint32_t w4 = w >> 4;
+#pragma unroll
+            for (int nt = 0; nt < NT2; ++nt) {
+              mma_u8u8(acc[pt][0][nt], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
+                       bu[nt][0], bu[nt][1]);
+              mma_u8u8(acc[pt][1][nt], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
+                       bu[nt][0], bu[nt][1]);
+            }
           }
         }
       }

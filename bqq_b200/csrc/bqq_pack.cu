@@ -62,7 +62,7 @@ __host__ __device__ inline uint32_t make_z_word(const Geom& g, const BitSource& 
   for (int e = 0; e < 4; ++e)
     for (int qh = 0; qh < 2; ++qh)
       for (int rr = 0; rr < 4; ++rr) {
-        const int k = 32 * x.blk1 + x.g + 8 * rr;
+        const int k = 32 * x.blk1 + 4 * x.g + rr;
         const int q = 32 * x.blk2 + 16 * qh + 4 * x.t + e;
         if (k < g.r && q < g.Q) word |= src.z(g, x.b, x.i, x.j, k, q) << (8 * e + 4 * qh + rr);
       }

@@ -5,10 +5,11 @@
 // reconstruct_W_kernel (src/bqq_cuda.cu:198-246).
 // A warp owns one 32x32 block of one patch and forms the counts Y Z on the tensor cores
 // (mma.sync m16n8k16, fp16 operands that are 2.0 or zero, fp32 accumulators: the sums are exact).  The Y plane word of a lane is already an A fragment (rows of Y over the rank);
-// the Z plane word is a fragment over q, so it is first turned into a B fragment over the rank: a 4x4
-// byte transposition between four lanes and a one-bit exchange between two, three shuffles in all.
+// the Z plane word is a fragment over q whose four rows are four consecutive ranks, exactly the four
+// ranks a lane of the B fragment needs for one column: the lane fetches the words of four plane lanes
+// (four shuffles) and expands one nibble per rank half and 8-column tile.
 // Row and column sums come from two more products with an all-ones operand, so one bit layer costs
-// 28 MMAs, 44 FMAs and about 80 integer instructions per warp.
+// 28 MMAs, 44 FMAs and about 90 integer instructions per warp.
 #include <algorithm>
 
 #include "bqq_common.cuh"
@@ -90,12 +91,12 @@ __device__ __forceinline__ void y_frag(uint32_t (&a)[4], uint32_t yw) {
   a[2] = bits_as_half2<4 * KH + R0, 1>(yw);
   a[3] = bits_as_half2<4 * KH + R0 + 1, 1>(yw);
 }
-// 8-column tile NT of the exchanged Z word, rank half KH
-template <int KH, int NT>
-__device__ __forceinline__ void z_frag(uint32_t (&b)[2], uint32_t zw) {
-  constexpr int pos = 4 * (NT >> 1) + 2 * KH + (NT & 1);
-  b[0] = bits_as_half2<pos, 0>(zw);
-  b[1] = bits_as_half2<pos, 1>(zw);
+// B fragment from a nibble m of a Z plane word: bits rr = 0..3 are Z[k0 + rr][q] for the four ranks of one lane of
+// the A fragment, whose k order is (0, 2 | 1, 3).  One multiplication moves bit 0 (1) to bit 14 and bit 2 (3) to
+// bit 30, the places where an fp16 pair reads 2.0; the other partial products fall outside the mask.
+__device__ __forceinline__ void z_frag(uint32_t (&b)[2], uint32_t m) {
+  b[0] = (m * 0x10004000u) & 0x40004000u;
+  b[1] = (m * 0x08002000u) & 0x40004000u;
 }
 
 // First word of Y and of Z (for the lane that reads plane lane `zsrc`) and first coefficient of one 32x32 block.
@@ -137,16 +138,13 @@ bqq_reconstruct_kernel(const ReconParams p) {
   const float scale = p.bound_parts ? p.scale * w_scale_from_bound(p.bound_parts, (float)(g.bw * g.r)) : p.scale;
   const float s_core = scale / (kBitValue * kBitValue), s_sum = scale / kBitValue;
   const size_t ldw = (size_t)g.cw * g.Q;
-  // Z word -> B fragment.  Name the bits of this lane b4..b0.  It reads the plane word of lane (b0 b3 b2 b1 b4),
-  // whose bit 8e + 4qh + rr is Z[k = 4 b0 + 2 b3 + b2 + 8 rr][q = 16 qh + 8 b1 + 4 b4 + e].  Exchanging the byte
-  // index e with (b3 b2) and bit 0 of rr with b1 leaves byte e' = Z[k = 16 rr1 + 8 b1 + 4 b0 + e'][q = 16 qh +
-  // 8 x + 4 b4 + 2 b3 + b2] at bit 4 qh + 2 rr1 + x of the byte: the B operand of column n = lane / 4 of the
-  // 8-column tile nt = 2 qh + x (q = 8 nt + n), rank half rr1, with the rank order of the Y fragment.
-  const int zsrc = (lane & 0x0E) | ((lane & 1) << 4) | (lane >> 4);
-  const uint32_t sel_a = (lane & 4) ? 0x3715u : 0x6240u;
-  const uint32_t sel_b = (lane & 8) ? 0x3276u : 0x5410u;
-  const uint32_t keep = (lane & 2) ? 0xAAAAAAAAu : 0x55555555u;
-  const int rot = (lane & 2) ? 31 : 1;
+  // Z word -> B fragments.  Plane lane 4 gz + tz holds, at bit 8e + 4qh + rr, Z[k = 4 gz + rr][q = 16 qh + 4 tz + e].
+  // Lane (n = g8, t = t4) of a B fragment needs, for rank half kh and 8-column tile nt = 2 qh + x, the ranks
+  // 16 kh + 4 t + rr of column q = 8 nt + n: the nibble at byte n & 3, half qh, of plane lane
+  // 16 kh + 4 t + 2 x + (n >> 2).  It reads the plane word of lane `lane` itself as its own Z word (zsrc = lane).
+  const int zsrc = lane;
+  const int zfrom = 4 * t4 + (g8 >> 2);               // + 16 kh + 2 x
+  const uint32_t zbyte = 0x4440u | (uint32_t)(g8 & 3);   // byte n & 3 into the low byte, zeros above
   const size_t ystep = (size_t)g.JG * g.PT * RT * 32 * kGroup, zstep = (size_t)g.JG * RT * g.QT * 32 * kGroup;
   const size_t cstep = (size_t)g.rw * g.cw;
 
@@ -220,21 +218,18 @@ bqq_reconstruct_kernel(const ReconParams p) {
           yw_n = nxt.y[0];
           zw_n = nxt.z[0];
         }
-        uint32_t o = __shfl_xor_sync(0xffffffffu, zw, 4);
-        zw = __byte_perm(zw, o, sel_a);
-        o = __shfl_xor_sync(0xffffffffu, zw, 8);
-        zw = __byte_perm(zw, o, sel_b);
-        o = __shfl_xor_sync(0xffffffffu, zw, 2);
-        o = __funnelshift_l(o, o, rot);
-        zw = (zw & keep) | (o & ~keep);
         // fragments of both rank halves: 16-row tile mt holds rows g8 + 8 (2 mt + h), 8-column tile nt columns 8 nt + n
         uint32_t a[2][2][4], bz[4][2][2];
         y_frag<0, 0>(a[0][0], yw); y_frag<1, 0>(a[0][1], yw);
         y_frag<0, 2>(a[1][0], yw); y_frag<1, 2>(a[1][1], yw);
-        z_frag<0, 0>(bz[0][0], zw); z_frag<1, 0>(bz[0][1], zw);
-        z_frag<0, 1>(bz[1][0], zw); z_frag<1, 1>(bz[1][1], zw);
-        z_frag<0, 2>(bz[2][0], zw); z_frag<1, 2>(bz[2][1], zw);
-        z_frag<0, 3>(bz[3][0], zw); z_frag<1, 3>(bz[3][1], zw);
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh)
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const uint32_t byte = __byte_perm(__shfl_sync(0xffffffffu, zw, zfrom + 16 * kh + 2 * x), 0u, zbyte);
+            z_frag(bz[x][kh], byte & 0xFu);          // qh = 0: tile x
+            z_frag(bz[2 + x][kh], byte >> 4);        // qh = 1: tile 2 + x
+          }
         // independent accumulation chains are interleaved: the second MMA of a chain waits for the first
         float d0[4], d1[4], dz[4];
         mma_f16_first(d0, a[0][0], kOnesHalf2, kOnesHalf2);                   // row sums

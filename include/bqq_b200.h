@@ -104,7 +104,7 @@ size_t bqq_algorithmic_bytes(const BqqDims* dims);
  *   yplanes [rw][NS][PT][RT][32 lanes][4 sub]
  * With lane = 4*g + t, a word is a 4-row x 8-column fragment in the order of the
  * int8 tensor-core operand that the decode kernel builds from it with byte masks:
- *   Z bit 8e + 4qh + rr = Z[k = 32rt + g + 8rr][q = 32qt + 16qh + 4t + e]
+ *   Z bit 8e + 4qh + rr = Z[k = 32rt + 4g + rr][q = 32qt + 16qh + 4t + e]
  *   Y bit 8e + 4kh + rr = Y[p = 32pt + g + 8rr][k = 32rt + 16kh + 4t + e]
  * All padding is zero.  ysum [bw,rw,cw,P] and zsum [bw,rw,cw,Q] (uint8; may be
  * NULL) are the row sums of Y and column sums of Z that the reference keeps as

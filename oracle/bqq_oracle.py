@@ -200,7 +200,7 @@ def popcount_matmul_u8(Yp, Zp):
 # Inside a 32x32 block a word belongs to a lane = 4*g + t (g = 0..7, t = 0..3)
 # and holds a 4-row x 8-column fragment arranged for the int8 tensor-core
 # operand that the decode kernel builds with byte masks:
-#   Z word bit 8*e + 4*qh + rr  =  Z[k = 32*rt + g + 8*rr][q = 32*qt + 16*qh + 4*t + e]
+#   Z word bit 8*e + 4*qh + rr  =  Z[k = 32*rt + 4*g + rr][q = 32*qt + 16*qh + 4*t + e]
 #   Y word bit 8*e + 4*kh + rr  =  Y[p = 32*pt + g + 8*rr][k = 32*rt + 16*kh + 4*t + e]
 # Word order: Z [rw][NS][RT][QT][32 lanes][4 sub], Y [rw][NS][PT][RT][32][4].
 
@@ -234,9 +234,9 @@ def pack_planes_u32(Y, Z):
     Yf = np.zeros((bw, rw, JG * GROUP, PT * 32, RT * 32), np.uint64)
     Zf[:, :, :cw, :r, :Q] = Z
     Yf[:, :, :cw, :P, :r] = Y
-    # rows = 32*blk + 8*rr + g ; cols = 32*blk + 16*half + 4*t + e
-    Zf = Zf.reshape(bw, rw, JG, GROUP, RT, 4, 8, QT, 2, 4, 4)     # b i jg sub rt rr g qt qh t e
-    Zf = Zf.transpose(1, 0, 2, 4, 7, 6, 9, 3, 10, 8, 5)           # i b jg rt qt g t sub e qh rr
+    # Z rows (ranks) = 32*blk + 4*g + rr ; Y rows = 32*blk + 8*rr + g ; cols = 32*blk + 16*half + 4*t + e
+    Zf = Zf.reshape(bw, rw, JG, GROUP, RT, 8, 4, QT, 2, 4, 4)     # b i jg sub rt g rr qt qh t e
+    Zf = Zf.transpose(1, 0, 2, 4, 7, 5, 9, 3, 10, 8, 6)           # i b jg rt qt g t sub e qh rr
     Zp = (Zf * _BITW).sum(axis=(-1, -2, -3)).astype(np.uint32)
     Yf = Yf.reshape(bw, rw, JG, GROUP, PT, 4, 8, RT, 2, 4, 4)     # b i jg sub pt rr g rt kh t e
     Yf = Yf.transpose(1, 0, 2, 4, 7, 6, 9, 3, 10, 8, 5)           # i b jg pt rt g t sub e kh rr
@@ -254,7 +254,7 @@ def unpack_planes_u32(Zp, Yp, bw, rw, cw, P, Q, r):
               + np.arange(4)[None, None, :]).astype(np.uint32)    # [e][half][rr]
     Zw = np.asarray(Zp, np.uint32).reshape(rw, bw, JG, RT, QT, 8, 4, GROUP)
     Zb = (Zw[..., None, None, None] >> shifts) & 1                # i b jg rt qt g t sub e qh rr
-    Zb = Zb.transpose(1, 0, 2, 7, 3, 10, 5, 4, 9, 6, 8)           # b i jg sub rt rr g qt qh t e
+    Zb = Zb.transpose(1, 0, 2, 7, 3, 5, 10, 4, 9, 6, 8)           # b i jg sub rt g rr qt qh t e
     Z = Zb.reshape(bw, rw, JG * GROUP, RT * 32, QT * 32)[:, :, :cw, :r, :Q].astype(bool)
     Yw = np.asarray(Yp, np.uint32).reshape(rw, bw, JG, PT, RT, 8, 4, GROUP)
     Yb = (Yw[..., None, None, None] >> shifts) & 1                # i b jg pt rt g t sub e kh rr
