@@ -45,8 +45,13 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   // may depend on the number of row patches.
   pl.bpc = (pl.variant == 0 && pl.NB == 1 && pl.nchunks == 1 && g.bw <= 4 && g.rw * g.bw * kDW <= 3072) ? g.bw : 1;
   pl.nparts = (g.bw / pl.bpc) * pl.nchunks;
+  // CTAs that take all bit layers of a short layer also prepare the x digits themselves (one launch).  Measured:
+  // letting the CTAs of chunked layers prepare their own chunk as well (no preparation kernel at all) is slower,
+  // 2048x6144 7.1 -> 9.4 us, 4096x14336 with 4 bit layers 23 -> 38 us: every CTA then starts with the read and
+  // quantisation of x before it can use its first plane words.
+  pl.self_prep = pl.bpc > 1 ? 1 : 0;
   const int PTv = kVariantPT[pl.variant], QTv = kVariantQT[pl.variant], RTv = kVariantRT[pl.variant];
-  pl.smem = (size_t)DecodeSmem(sgw, pl.NB, PTv, QTv, RTv, pl.bpc).total;
+  pl.smem = (size_t)DecodeSmem(sgw, pl.NB, PTv, QTv, RTv, pl.bpc, pl.self_prep != 0).total;
   const size_t Mp = (size_t)pl.mtiles * pl.NB, cwp = (size_t)g.JG * kGroup;
   pl.xdig_bytes = align_up(Mp * cwp * 2 * QTv * 32, 256);
   pl.xmeta_bytes = 3 * align_up(Mp * cwp * 4, 256);     // scale, sum, l1
@@ -60,7 +65,7 @@ int decode_launches(const BqqDims* dims, int M) {
   Geom g(*dims);
   DecodePlan pl = make_decode_plan(g, M);
   if (pl.variant < 0) return BQQ_ERR_UNSUPPORTED;
-  return pl.bpc > 1 ? 1 : 2;
+  return pl.self_prep ? 1 : 2;
 }
 
 size_t decode_workspace_bytes(const BqqDims* dims, int M) {

@@ -54,6 +54,9 @@ namespace bqq {
 #ifndef BQQ_NB4_REGS
 #define BQQ_NB4_REGS 80
 #endif
+#ifndef BQQ_NB1_REGS
+#define BQQ_NB1_REGS 72
+#endif
 constexpr int kDW = 4;                   // warps per CTA
 constexpr int kDT = kDW * 32;
 constexpr int kMaxCounters = 65536;      // fixed-size counter region at the start of the workspace
@@ -65,6 +68,7 @@ struct DecodePlan {
   int mtiles;      // ceil(M / NB)
   int sgw;         // super-groups per warp
   int bpc;         // bit layers per CTA (kDW warps each): 1, or all of them for short single-chunk layers
+  int self_prep;   // 1: the decode CTAs prepare x themselves (one launch); 0: a preparation kernel runs first
   int nchunks;     // chunks per bit layer
   int nparts;      // partial sums per output = (bw / bpc) * nchunks
   size_t smem;
@@ -134,9 +138,11 @@ __device__ __forceinline__ uint32_t pick(const uint4& v, int sub) {
 }
 
 constexpr int kMaxSgw = 32;              // upper bound of super-groups per warp (resident coefficients: 64 B each)
-// u digit exchange at M = 1, per 32-rank block: 128 words [digit d][lane group G' = G ^ 4 (d & 1)][sub], G = 0..7 the
-// lane group g that produced the word (ranks 4G .. 4G+3).  Producers (fixed d, all G and sub) and consumers (128-bit
-// loads over sub for G in 0..3 or 4..7 and two neighbouring digits) both touch every bank once.
+// u digit exchange at M = 1, per 32-rank block: 128 words.  The word of digit d, lane group G (ranks 4G .. 4G+3,
+// produced by the lanes with g = G) and col patch sub sits at
+//   32 d + 4 ((2 (G & 3) + (sub >> 1) + (d & 1)) & 7) + 2 (sub & 1) + (G >> 2),
+// so that a 128-bit load gives a consumer (b0, b1) of two col patches in operand order (b0: G = t, b1: G = t + 4)
+// and both the producers' stores (fixed d) and the consumers' loads (two neighbouring digits) touch every bank once.
 constexpr int kUBlock = 128;
 
 // Shared-memory carve-up (bytes), shared by host plan and kernel.  Per warp a ring of `stages`
@@ -144,7 +150,8 @@ constexpr int kUBlock = 128;
 // Resident for the whole chunk: coefficients and x statistics (one mbarrier).
 struct DecodeSmem {
   int bars, ring, slot, stages, yoff, xoff, coef, meta, udig, red, xres, xstat, total;
-  __host__ __device__ constexpr DecodeSmem(int sgw, int NB, int PT, int QT, int RT, int bpc = 1)
+  // xp: the CTA prepares x itself (digits and statistics of its chunk live in shared memory)
+  __host__ __device__ constexpr DecodeSmem(int sgw, int NB, int PT, int QT, int RT, int bpc = 1, bool xp = false)
       : bars(0), ring(0), slot(0), stages(0), yoff(0), xoff(0), coef(0), meta(0), udig(0), red(0), xres(0), xstat(0),
         total(0) {
     const int nsg = kDW * sgw;                        // super-groups per chunk
@@ -162,9 +169,9 @@ struct DecodeSmem {
     // more rows: bytes [warps][4 sub][NB][4 digits][RP] (+ 16 bytes of padding per row of X)
     udig = o;  o += nwarps * (NB == 1 ? RT * kUBlock * 4 : kGroup * NB * (4 * RT * 32 + 16));
     red = o;   o += nwarps * NB * PT * 32 * 4;        // f32 [warps][NB][PP]
-    // CTAs that take all bit layers prepare x themselves: digits and statistics of the whole chunk
-    xres = o;  o += bpc > 1 ? nsg * NB * 2 * QT * 128 : 0;   // uint4 [nsg][NB][digit][QT][8]
-    xstat = o; o += bpc > 1 ? 3 * nsg * 16 : 0;              // float [scale|sum|l1][nsg*4]
+    // CTAs that prepare x themselves: digits and statistics of the whole chunk
+    xres = o;  o += xp ? nsg * NB * 2 * QT * 128 : 0;        // uint4 [nsg][NB][digit][QT][8]
+    xstat = o; o += xp ? 3 * nsg * 16 : 0;                   // float [scale|sum|l1][nsg*4]
     total = o;
   }
 };
@@ -218,9 +225,11 @@ __device__ __forceinline__ float row_sumsq_share(const XSource& s, int m, int ti
   return acc;                                       // the warp's share, in every lane
 }
 
+// `jsrc` is the col patch whose x is read, `j` its place in the output (they differ when a CTA prepares only
+// its own chunk: j counts from the chunk's first col patch, a multiple of 4).
 template <int QT>
 __device__ __forceinline__ void xprep_pair(const XSource& xs, float inv_rms, int Q, int NB, int JG,
-                                           bool write, bool live, int m, int j, int mtile, int beta, int sub8,
+                                           bool write, bool live, int m, int jsrc, int j, int mtile, int beta, int sub8,
                                            uint32_t* __restrict__ words, float* __restrict__ xscale,
                                            float* __restrict__ xsum, float* __restrict__ xl1, int stat) {
   float v[4 * QT];
@@ -228,7 +237,7 @@ __device__ __forceinline__ void xprep_pair(const XSource& xs, float inv_rms, int
 #pragma unroll
   for (int e = 0; e < 4 * QT; ++e) {
     const int q = sub8 * 4 * QT + e;
-    v[e] = (live && q < Q) ? load_x(xs, m, j * Q + q, inv_rms) : 0.f;
+    v[e] = (live && q < Q) ? load_x(xs, m, jsrc * Q + q, inv_rms) : 0.f;
     amax = fmaxf(amax, fabsf(v[e]));
     sum += v[e];
     l1 += fabsf(v[e]);
@@ -287,7 +296,7 @@ bqq_xprep_kernel(const XSource xs, int M, int cw, int Q, int cwp, int NB,
   }
   const int j = (blockIdx.x * 128 + threadIdx.x) >> 3;
   const bool inside = j < cwp;
-  xprep_pair<QT>(xs, inv_rms, Q, NB, cwp / kGroup, inside, inside && m < M && j < cw, m, inside ? j : 0, m / NB, m % NB,
+  xprep_pair<QT>(xs, inv_rms, Q, NB, cwp / kGroup, inside, inside && m < M && j < cw, m, inside ? j : 0, inside ? j : 0, m / NB, m % NB,
                  threadIdx.x & 7, reinterpret_cast<uint32_t*>(xdig), xscale, xsum, xl1, m * cwp + j);
 }
 
@@ -318,9 +327,10 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
     peer_slot_store(p.peer_regions[q] + off, word, seq);
 }
 
-// MB: the CTA takes all bit layers of its row patch (4 warps each) instead of one.
+// MB: the CTA prepares x itself (no preparation kernel ran) and takes p.bpc bit layers of its row patch (4 warps
+// each): all of them for short single-chunk layers, else one.
 template <int PT, int QT, int RT, int NB, bool MB>
-__global__ void __maxnreg__(PT == 1 ? (NB == 1 ? (MB ? 80 : 72) : BQQ_NB4_REGS) : 255)
+__global__ void __maxnreg__(PT == 1 ? (NB == 1 ? (MB ? 80 : BQQ_NB1_REGS) : BQQ_NB4_REGS) : 255)
 bqq_decode_kernel(const DecodeParams p) {
   const int bpc = MB ? p.bpc : 1;
   constexpr int RP = RT * 32;
@@ -328,7 +338,7 @@ bqq_decode_kernel(const DecodeParams p) {
   constexpr int NT2 = NB == 1 ? 1 : 2;              // n-tiles of the second contraction
   extern __shared__ __align__(128) uint8_t sm[];
   const int nsg = kDW * p.sgw;                      // super-groups per chunk (pitch of the resident arrays)
-  const DecodeSmem L(p.sgw, NB, PT, QT, RT, bpc);
+  const DecodeSmem L(p.sgw, NB, PT, QT, RT, bpc, MB);
   constexpr int S = DecodeSmem(1, NB, PT, QT, RT).stages;
   constexpr int kSlot = DecodeSmem(1, NB, PT, QT, RT).slot;
   constexpr int kYoff = DecodeSmem(1, NB, PT, QT, RT).yoff / 16, kXoff = DecodeSmem(1, NB, PT, QT, RT).xoff / 16;
@@ -428,9 +438,11 @@ bqq_decode_kernel(const DecodeParams p) {
       inv_rms = rsqrtf(tot / (float)xs.n_in + p.eps);
       __syncthreads();                               // red is reused for the warps' sums at the end
     }
-    for (int pair = tid >> 3; pair < nsg * kGroup; pair += (kDT * bpc) >> 3)
-      xprep_pair<QT>(xs, inv_rms, p.Q, NB, nsg, true, pair < p.cw && m0 < p.M, m0, pair, 0, 0, tid & 7,
+    for (int pair = tid >> 3; pair < nsg * kGroup; pair += (kDT * bpc) >> 3) {
+      const int j = jg0 * kGroup + pair;             // col patch of the layer; `pair` counts inside the chunk
+      xprep_pair<QT>(xs, inv_rms, p.Q, NB, nsg, true, j < p.cw && m0 < p.M, m0, j, pair, 0, 0, tid & 7,
                      reinterpret_cast<uint32_t*>(sm + L.xres), st, st + nsg * 4, st + nsg * 8, pair);
+    }
     __syncthreads();
   } else {
     // the x digits and statistics come from the preparation kernel launched just before this one
@@ -567,16 +579,18 @@ bqq_decode_kernel(const DecodeParams p) {
   const int xlane = kXoff + g * (QT * 8) + t;                                          // uint4 index (M > 1)
   const float* mrow = smeta + my_beta * 3 * nsg * 4;   // [alpha | beta | gamma] of this lane's row of X
   // where the lane's u digits go ...
-  uint8_t* ust = NB == 1 ? my_udig + 4 * lane : my_udig + t * kURow + 4 * g;   // M = 1: word 4G + sub of digit 0
+  // M = 1: word of digit 0 (digit 2: + 64 words; digit 1: the 16-byte group index is one higher, modulo 8)
+  uint8_t* ust = NB == 1 ? my_udig + 4 * (8 * (g & 3) + 2 * t + (g >> 2)) : my_udig + t * kURow + 4 * g;
+  const int ust1 = 32 + 4 * ((2 * (g & 3) + (t >> 1) + 1) & 7) + 2 * (t & 1) + (g >> 2) - (8 * (g & 3) + 2 * t + (g >> 2));
   // ... and where its B operand of the second contraction comes from
   const uint8_t* uld[NT2];
 #pragma unroll
   for (int nt = 0; nt < NT2; ++nt) {
     const int beta = 2 * nt + (g >> 2);                  // M > 1: row of X and digit of column n = g
-    uld[nt] = NB == 1 ? my_udig + 4 * (32 * (g & 3) + 4 * t) : my_udig + beta * kURow + (g & 3) * RP + 4 * t;
+    uld[nt] = NB == 1 ? my_udig + 4 * (32 * (g & 3)) : my_udig + beta * kURow + (g & 3) * RP + 4 * t;
   }
-  // M = 1: the words of lane groups t (ranks 4t ..: first half of k) and t + 4 (second half) of digit g & 3
-  const int ulo = (g & 1) ? 64 : 0, uhi = 64 - ulo;      // byte offsets from uld[0]
+  // M = 1: byte offsets from uld[0] of the two 128-bit groups of digit g & 3: col patches 0, 1 and 2, 3
+  const int u01 = 16 * ((2 * t + (g & 1)) & 7), u23 = 16 * ((2 * t + 1 + (g & 1)) & 7);
 #pragma unroll(NB == 1 ? 4 : 1)
   for (int n = 0; n < nw; ++n) {
     // refill the slot consumed in the previous iteration with the super-group S - 1 ahead
@@ -649,7 +663,7 @@ bqq_decode_kernel(const DecodeParams p) {
         const uint32_t p23a = __byte_perm(D[2], D[3], 0x5140), p23b = __byte_perm(D[2], D[3], 0x6262);
         uint32_t* dst = reinterpret_cast<uint32_t*>(ust) + rt * kUBlock;
         dst[0] = __byte_perm(p01a, p23a, 0x5410);
-        dst[32 + (lane ^ 16) - lane] = __byte_perm(p01a, p23a, 0x7632);
+        dst[ust1] = __byte_perm(p01a, p23a, 0x7632);
         dst[64] = __byte_perm(p01b, p23b, 0x5410);
       }
       __syncwarp();
@@ -657,8 +671,10 @@ bqq_decode_kernel(const DecodeParams p) {
       // ---- second contraction: V[p][digit] += sum_k Y[p][k] udigit[k] --------------------
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt) {
-        const uint4 bu0 = *reinterpret_cast<const uint4*>(uld[0] + rt * 4 * kUBlock + ulo);
-        const uint4 bu1 = *reinterpret_cast<const uint4*>(uld[0] + rt * 4 * kUBlock + uhi);
+        // (b0, b1) of col patches 0, 1 and of col patches 2, 3: already in operand order
+        const uint4 bu01 = *reinterpret_cast<const uint4*>(uld[0] + rt * 4 * kUBlock + u01);
+        const uint4 bu23 = *reinterpret_cast<const uint4*>(uld[0] + rt * 4 * kUBlock + u23);
+        const uint32_t bu[kGroup][2] = {{bu01.x, bu01.y}, {bu01.z, bu01.w}, {bu23.x, bu23.y}, {bu23.z, bu23.w}};
 #pragma unroll
         for (int sub = 0; sub < kGroup; ++sub) {
 #pragma unroll
@@ -666,9 +682,9 @@ bqq_decode_kernel(const DecodeParams p) {
             const uint32_t w = pick(yw[pt][rt], sub);
             const uint32_t w4 = w >> 4;
             mma_u8u8(acc[pt][0][0], w & 0x01010101u, w & 0x02020202u, w4 & 0x01010101u, w4 & 0x02020202u,
-                     pick(bu0, sub), pick(bu1, sub));
+                     bu[sub][0], bu[sub][1]);
             mma_u8u8(acc[pt][1][0], w & 0x04040404u, w & 0x08080808u, w4 & 0x04040404u, w4 & 0x08080808u,
-                     pick(bu0, sub), pick(bu1, sub));
+                     bu[sub][0], bu[sub][1]);
           }
         }
       }
@@ -884,13 +900,13 @@ bqq_decode_kernel(const DecodeParams p) {
 
 template <int PT, int QT, int RT, int NB>
 static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cudaStream_t st) {
-  auto kern = (PT == 1 && NB == 1 && p.bpc > 1) ? bqq_decode_kernel<PT, QT, RT, NB, (PT == 1 && NB == 1)>
-                                                : bqq_decode_kernel<PT, QT, RT, NB, false>;
+  auto kern = (PT == 1 && NB == 1 && pl.self_prep) ? bqq_decode_kernel<PT, QT, RT, NB, (PT == 1 && NB == 1)>
+                                                   : bqq_decode_kernel<PT, QT, RT, NB, false>;
   if (pl.smem > 48 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) != cudaSuccess)
       return BQQ_ERR_CUDA;
   }
-  const bool merged = PT == 1 && NB == 1 && p.bpc > 1;   // such CTAs prepare x themselves
+  const bool merged = PT == 1 && NB == 1 && pl.self_prep;   // such CTAs prepare x themselves
   // Every kernel is launched as a programmatic dependent of whatever precedes it in the stream: it may
   // become resident while that kernel still runs, prefetches weights, and executes griddepcontrol.wait
   // before it reads activations or touches the workspace.  After a kernel that never triggers early
