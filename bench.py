@@ -469,12 +469,18 @@ def extra_sweep_batched(layers, cfgs, device, stream, steps):
     return out
 
 
-def extra_large_layer(device, rank, world, peer, stream):
+def extra_large_layer(device, rank, world, peer_factory, stream):
     """Bit-depth-extended large layers: 2+1 bit layers (the added one with N(0,0.005) coefficients), P=Q=r=64,
     bf16 activations, batch 1 and 32, row patches sharded over the ranks, outputs gathered on every rank."""
     import torch
     import torch.distributed as dist
     out = {}
+    peer = None
+    if world > 1:
+        try:
+            peer = peer_factory(28672 * 2)              # one gathered row of the widest output
+        except RuntimeError:
+            peer = None
     for (o, i) in ((8192, 28672), (28672, 8192)):
         layer = make_layer(o // world, i, 3, device, seed=50 + rank, group=64, rank=64, last_bit_scale=0.005)
         drop_bool_factors(layer)
@@ -519,6 +525,9 @@ def extra_large_layer(device, rank, world, peer, stream):
                                     'gather': 'none' if world == 1 else ('peer stores' if peer is not None and M <= 16 else 'nccl')}
         del layer, flush
         torch.cuda.empty_cache()
+    if peer is not None:
+        peer.status()
+        peer.close()
     out['note'] = ('whole-layer algorithmic bytes / max-over-ranks time of one forward incl. the gather; '
                    'L2 flushed between timed forwards; eager launches (no graph)')
     return out
@@ -795,7 +804,7 @@ def main():
     hbm_peak, bf16_peak, peak_kind = peaks()
     if not args.no_extras:
         with torch.cuda.stream(stream):
-            extras['large_layer'] = extra_large_layer(device, rank, world, peer, stream)
+            extras['large_layer'] = extra_large_layer(device, rank, world, peer_factory, stream)
         if rank == 0:
             extras['prefill'] = extra_prefill(device, bf16_peak)
         if world > 1:
@@ -826,8 +835,8 @@ def main():
                        'steps_per_graph_launch': group,
                        'l2': 'working set per step (208.5 MB of packed planes) exceeds the 126 MB L2',
                        'parallelism': 'single GPU' if world == 1 else (
-                           f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel '
-                           '(bqq_forward_decode_gathered)' if peer is not None else
+                           f'row-patch shards x{world}, outputs stored to the peers from the epilogue of the decode kernel and '
+                           'received by a few more CTAs of the same launch (bqq_forward_decode_gathered)' if peer is not None else
                            f'row-patch shards x{world}, NCCL all-gather of outputs (peer gather set-up failed)')},
             'timing': {'blocks': len(blocks), 'block_steps': args.steps, 'median_block_ms': ms,
                        'min_block_ms': blk_min, 'max_block_ms': blk_max,
@@ -837,8 +846,8 @@ def main():
                     'd2h_bytes_per_step': sum(world * o * 2 for (o, i, bw) in cfgs),
                     'steps': e2e_steps, 'ms_per_step': e2e_ms / e2e_steps,
                     'route': 'bqq_forward_host (module.bind_host)' if world == 1 else e2e_route},
-            # decode kernel (+ activation preparation kernel) per layer, + the gather kernel when sharded
-            'gpu_launches': (launches_per_step + (len(cfgs) if peer is not None else 0)) * args.steps,
+            # decode kernel (+ activation preparation kernel) per layer; the gather runs inside the decode launch
+            'gpu_launches': launches_per_step * args.steps,
             'roofline': {'bound': 'hbm', 'achieved': per_gpu, 'peak': hbm_peak, 'unit': 'GB/s',
                          'frac': per_gpu / hbm_peak, 'traffic': TRAFFIC_RATIO * step_bytes / len(cfgs),
                          'traffic_note': 'constant from profiles: dram read+write bytes of one ncu capture (4096x14336, '

@@ -48,11 +48,11 @@ int bqq_decode_check_args(const BqqLayer* layer, const void* x, int x_dtype, int
 // bqq_forward_decode, optionally with the peer stores of bqq_forward_decode_gathered (not exported in the header)
 int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
                             int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
-                            const BqqFusion* fusion = nullptr) {
+                            const BqqFusion* fusion = nullptr, void* gathered = nullptr, int64_t ld_gathered = 0) {
   const int rc = bqq_decode_check_args(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, fusion);
   if (rc) return rc;
   return decode_launch(layer, x, x_dtype, M, ldx, y, y_dtype, ldy, workspace, workspace_bytes,
-                       (cudaStream_t)stream, peer, fusion);
+                       (cudaStream_t)stream, peer, fusion, gathered, ld_gathered);
 }
 
 extern "C" {

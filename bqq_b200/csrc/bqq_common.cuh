@@ -144,7 +144,8 @@ inline int launch_status() {
 // `peer` (may be NULL): the decode kernel also stores its outputs into the peers' gather regions
 int decode_launch(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                   int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream,
-                  const BqqPeerGroup* peer = nullptr, const BqqFusion* fusion = nullptr);
+                  const BqqPeerGroup* peer = nullptr, const BqqFusion* fusion = nullptr,
+                  void* gathered = nullptr, int64_t ld_gathered = 0);   // with `peer`: the gathered rows [M, world * out]
 size_t peer_half_bytes(size_t gather_bytes);   // bytes of one half of a peer region's slot area
 size_t decode_workspace_bytes(const BqqDims* dims, int M);
 constexpr size_t kPeerCtrlBytes = 512;   // control words at the start of a peer gather region (bqq_peer.cu)

@@ -77,9 +77,10 @@ size_t decode_workspace_bytes(const BqqDims* dims, int M) {
 
 int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                   int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t st, const BqqPeerGroup* peer,
-                  const BqqFusion* fusion) {
+                  const BqqFusion* fusion, void* gathered, int64_t ld_gathered) {
   Geom g(L->dims);
   DecodePlan pl = make_decode_plan(g, M);
+  pl.nrecv = 0;
   if (pl.variant < 0) return BQQ_ERR_UNSUPPORTED;
   if ((size_t)g.rw * pl.mtiles > (size_t)kMaxCounters - 1) return BQQ_ERR_UNSUPPORTED;   // last word: status
   if ((size_t)g.bw * g.rw * g.cw >= (1ull << 31)) return BQQ_ERR_UNSUPPORTED;           // 32-bit coefficient offsets
@@ -124,6 +125,9 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
   for (int q = 0; q < BQQ_MAX_PEERS; ++q) p.peer_regions[q] = nullptr;
   p.peer_world = p.peer_rank = p.peer_row_words = 0;
   p.peer_half = 0;
+  p.peer_out = nullptr;
+  p.peer_ld_out = p.peer_wait = 0;
+  p.ncompute = g.rw * (g.bw / pl.bpc) * pl.nchunks;
   if (peer) {
     const size_t es = dtype_size(y_dtype);
     if (((size_t)g.out_features() * es) % 4 || (es == 2 && (g.P & 1))) return BQQ_ERR_MISALIGNED;   // outputs travel as 32-bit words
@@ -132,6 +136,15 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
     p.peer_rank = peer->rank;
     p.peer_row_words = (int)((size_t)g.out_features() * es / 4);
     p.peer_half = peer_half_bytes(peer->gather_bytes);
+    // the receiving side runs in the same launch: a few CTAs that poll this rank's region and write the rows
+    if (!gathered) return BQQ_ERR_NULL;
+    if ((((size_t)ld_gathered * es) % 4) || ((uintptr_t)gathered & 3)) return BQQ_ERR_MISALIGNED;
+    p.peer_out = reinterpret_cast<uint32_t*>(gathered);
+    p.peer_ld_out = (long long)((size_t)ld_gathered * es / 4);
+    p.peer_wait = peer->wait_cycles ? (long long)peer->wait_cycles : 2000000000LL;
+    const long long words = (long long)M * p.peer_row_words * peer->world;
+    const int threads = kDT * pl.bpc;
+    pl.nrecv = (int)std::min<long long>(8, std::max<long long>(1, (words + 2 * threads - 1) / (2 * threads)));
   }
   switch (pl.variant) {
     case 0: return decode_launch_variant<0>(p, pl, st);

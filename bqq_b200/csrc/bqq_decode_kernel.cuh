@@ -69,6 +69,7 @@ struct DecodePlan {
   int sgw;         // super-groups per warp
   int bpc;         // bit layers per CTA (kDW warps each): 1, or all of them for short single-chunk layers
   int self_prep;   // 1: the decode CTAs prepare x themselves (one launch); 0: a preparation kernel runs first
+  int nrecv;       // receiving CTAs appended to the grid (peer gather in the same launch), else 0
   int nchunks;     // chunks per bit layer
   int nparts;      // partial sums per output = (bw / bpc) * nchunks
   size_t smem;
@@ -107,6 +108,12 @@ struct DecodeParams {
   uint8_t* peer_regions[BQQ_MAX_PEERS];
   int peer_world, peer_rank, peer_row_words;
   unsigned long long peer_half;
+  // ... and the receiving side in the same launch: the CTAs blockIdx.x >= ncompute only wait for every rank's
+  // words in this rank's region and write the gathered rows [M][world * row words] to peer_out
+  uint32_t* peer_out;
+  long long peer_ld_out;     // row pitch of peer_out in 32-bit words
+  long long peer_wait;       // clock budget of one wait on a peer
+  int ncompute;              // CTAs along x that compute (the rest receive)
   int coef_vec;            // 1: fp32 coefficients, cw % 4 == 0, 16-byte aligned -> 128-bit loads
 };
 
@@ -213,12 +220,68 @@ __device__ __forceinline__ float load_x(const XSource& s, int m, int n, float in
   }
   return v;
 }
+// Four consecutive elements n0 .. n0+3 of a tensor of type `dt` as floats; one 8- or 16-byte load when the
+// address allows it, four element loads otherwise.
+__device__ __forceinline__ void load_quad(const void* base, size_t idx, int dt, float (&v)[4]) {
+  if (dt == BQQ_F32) {
+    const float* p = reinterpret_cast<const float*>(base) + idx;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+      const float4 q = *reinterpret_cast<const float4*>(p);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = p[e];
+    }
+    return;
+  }
+  const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + idx;
+  uint32_t w0, w1;
+  if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+    const uint2 q = *reinterpret_cast<const uint2*>(p);
+    w0 = q.x; w1 = q.y;
+  } else {
+    w0 = (uint32_t)p[0] | ((uint32_t)p[1] << 16);
+    w1 = (uint32_t)p[2] | ((uint32_t)p[3] << 16);
+  }
+  if (dt == BQQ_BF16) {
+    v[0] = __uint_as_float(w0 << 16); v[1] = __uint_as_float(w0 & 0xFFFF0000u);
+    v[2] = __uint_as_float(w1 << 16); v[3] = __uint_as_float(w1 & 0xFFFF0000u);
+  } else {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w0));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w1));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+}
+// x[m, n0 .. n0+3] after the prologue (all four columns exist)
+__device__ __forceinline__ void load_x_quad(const XSource& s, int m, int n0, float inv_rms, float (&v)[4]) {
+  load_quad(s.x, (size_t)m * s.ld + n0, s.dtype, v);
+  if (s.mode == BQQ_PRO_RMSNORM) {
+    float w[4];
+    load_quad(s.w, n0, s.w_dtype, w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = v[e] * inv_rms * w[e];
+  } else if (s.mode == BQQ_PRO_SWIGLU) {
+    float u[4];
+    load_quad(s.x, (size_t)m * s.ld + s.n_in + n0, s.dtype, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = v[e] / (1.f + __expf(-v[e])) * u[e];
+  }
+}
 // Sum of squares of row m over this thread's share of the columns (threads tid, tid + n, ...).
 __device__ __forceinline__ float row_sumsq_share(const XSource& s, int m, int tid, int nthreads) {
   float acc = 0.f;
-  for (int n = tid; n < s.n_in; n += nthreads) {
-    const float v = load_as_float(s.x, (size_t)m * s.ld + n, s.dtype);
-    acc = fmaf(v, v, acc);
+  if ((s.n_in & 3) == 0) {
+    for (int n = 4 * tid; n < s.n_in; n += 4 * nthreads) {
+      float v[4];
+      load_quad(s.x, (size_t)m * s.ld + n, s.dtype, v);
+      acc = fmaf(v[0], v[0], acc); acc = fmaf(v[1], v[1], acc);
+      acc = fmaf(v[2], v[2], acc); acc = fmaf(v[3], v[3], acc);
+    }
+  } else {
+    for (int n = tid; n < s.n_in; n += nthreads) {
+      const float v = load_as_float(s.x, (size_t)m * s.ld + n, s.dtype);
+      acc = fmaf(v, v, acc);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -235,12 +298,23 @@ __device__ __forceinline__ void xprep_pair(const XSource& xs, float inv_rms, int
   float v[4 * QT];
   float amax = 0.f, sum = 0.f, l1 = 0.f;
 #pragma unroll
-  for (int e = 0; e < 4 * QT; ++e) {
-    const int q = sub8 * 4 * QT + e;
-    v[e] = (live && q < Q) ? load_x(xs, m, jsrc * Q + q, inv_rms) : 0.f;
-    amax = fmaxf(amax, fabsf(v[e]));
-    sum += v[e];
-    l1 += fabsf(v[e]);
+  for (int w4 = 0; w4 < QT; ++w4) {
+    const int q0 = sub8 * 4 * QT + 4 * w4;
+    float quad[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live && q0 + 4 <= Q) {
+      load_x_quad(xs, m, jsrc * Q + q0, inv_rms, quad);
+    } else if (live) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (q0 + e < Q) quad[e] = load_x(xs, m, jsrc * Q + q0 + e, inv_rms);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[4 * w4 + e] = quad[e];
+      amax = fmaxf(amax, fabsf(quad[e]));
+      sum += quad[e];
+      l1 += fabsf(quad[e]);
+    }
   }
 #pragma unroll
   for (int o = 1; o < 8; o <<= 1) {
@@ -327,11 +401,60 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
     peer_slot_store(p.peer_regions[q] + off, word, seq);
 }
 
+// Receiving CTAs of a gathered decode launch (blockIdx.x >= ncompute): poll every slot of this rank's region until
+// it carries the gather's sequence number (bounded), write the data words to the caller's tensor.  They run beside
+// the computing CTAs of the same launch, which never wait for them.
+static __device__ __noinline__ void peer_receive(const DecodeParams& p) {
+  __shared__ int s_giveup;
+  // the output tensor may still be read by earlier kernels of the stream; later kernels need not wait for the polling
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int tid = threadIdx.x;
+  if (tid == 0) s_giveup = 0;
+  __syncthreads();
+  unsigned* mine = reinterpret_cast<unsigned*>(p.peer_regions[p.peer_rank]);
+  if (blockIdx.y == 0) {
+    const unsigned count = *reinterpret_cast<volatile unsigned*>(mine) + 1u;
+    const unsigned e = count | 0x80000000u;
+    const uint8_t* slots = reinterpret_cast<const uint8_t*>(mine) + kPeerCtrlBytes + (count & 1u) * p.peer_half;
+    const long long grow = (long long)p.peer_row_words * p.peer_world;
+    const long long n = (long long)p.M * grow;
+    const long long step = (long long)(gridDim.x - p.ncompute) * blockDim.x;
+    for (long long w = (long long)(blockIdx.x - p.ncompute) * blockDim.x + tid; w < n; w += step) {
+      uint2 v = peer_slot_load(slots + 8 * w);
+      if (v.y != e) {
+        const long long t0 = clock64();
+        while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
+          if (clock64() - t0 > p.peer_wait) { s_giveup = 1; break; }
+          v = peer_slot_load(slots + 8 * w);
+        }
+      }
+      const long long r = w / grow, c = w - r * grow;
+      p.peer_out[r * p.peer_ld_out + c] = v.x;
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && blockIdx.y == 0) {
+    if (s_giveup) atomicExch(mine + 1, 1u);
+    // Every word of this gather has arrived, so every sender of this rank has read the gather count (a sender reads
+    // it before its first store): the last receiving CTA may advance it.  Computing CTAs take no part in this.
+    __threadfence();
+    if (atomicAdd(mine + 2, 1u) == gridDim.x - p.ncompute - 1u) {
+      mine[2] = 0u;
+      *reinterpret_cast<volatile unsigned*>(mine) = *reinterpret_cast<volatile unsigned*>(mine) + 1u;
+    }
+  }
+}
+
 // MB: the CTA prepares x itself (no preparation kernel ran) and takes p.bpc bit layers of its row patch (4 warps
 // each): all of them for short single-chunk layers, else one.
 template <int PT, int QT, int RT, int NB, bool MB>
 __global__ void __maxnreg__(PT == 1 ? (NB == 1 ? (MB ? 80 : BQQ_NB1_REGS) : BQQ_NB4_REGS) : 255)
 bqq_decode_kernel(const DecodeParams p) {
+  if (p.peer_world && (int)blockIdx.x >= p.ncompute) {
+    peer_receive(p);
+    return;
+  }
   const int bpc = MB ? p.bpc : 1;
   constexpr int RP = RT * 32;
   constexpr int PP = PT * 32;
@@ -927,7 +1050,8 @@ static int launch_decode_variant(const DecodeParams& p, const DecodePlan& pl, cu
                            const_cast<float*>(p.xl1)) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.rw * (p.bw / p.bpc) * p.nchunks, pl.mtiles);
+  // p.ncompute computing CTAs along x; with a peer gather a few more that only receive
+  cfg.gridDim = dim3(p.ncompute + pl.nrecv, pl.mtiles);
   cfg.blockDim = dim3(kDT * p.bpc);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = st;

@@ -25,7 +25,7 @@
 // bqq_forward_decode with the peer group handed through to the kernel (bqq_api.cu)
 int bqq_forward_decode_peer(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
                             int64_t ldy, void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
-                            const BqqFusion* fusion = nullptr);
+                            const BqqFusion* fusion = nullptr, void* gathered = nullptr, int64_t ld_gathered = 0);
 
 namespace bqq {
 
@@ -221,12 +221,12 @@ int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtyp
   const size_t es = dtype_size(y_dtype);
   if (!es) return BQQ_ERR_DTYPE;
   if ((size_t)M * geo.out_features() * g->world * es > g->gather_bytes) return BQQ_ERR_WORKSPACE;
-  // same argument checks as bqq_forward_decode, then the decode kernel with the peer stores in its
-  // epilogue, then the receiving kernel (programmatic dependent: it polls while the decode kernel ends)
-  int rc = bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y_local, y_dtype, ldy, workspace, workspace_bytes, stream, g,
-                                   fusion);
-  if (rc) return rc;
-  return peer_gather_launch(g, nullptr, y_dtype, M, geo.out_features(), geo.out_features(), gathered, ld_gathered, stream);
+  if (ld_gathered < (int64_t)geo.out_features() * g->world) return BQQ_ERR_BAD_SHAPE;
+  // same argument checks as bqq_forward_decode, then ONE launch: the decode kernel's computing CTAs store their
+  // finished row patches into every rank's region, a few more CTAs of the same grid wait for the peers' row
+  // patches and write the gathered rows
+  return bqq_forward_decode_peer(layer, x, x_dtype, M, ldx, y_local, y_dtype, ldy, workspace, workspace_bytes, stream, g,
+                                 fusion, gathered, ld_gathered);
 }
 
 int bqq_peer_status(const BqqPeerGroup* g, void* stream) {

@@ -321,17 +321,17 @@ int bqq_peer_gather(const BqqPeerGroup* group, const void* y_local, int dtype, i
 int bqq_peer_status(const BqqPeerGroup* group, void* stream);
 
 /*
- * bqq_forward_decode of a row-patch shard fused with the gather: the decode
- * kernel's epilogue stores every finished output row patch into the gather
- * regions of all ranks while the rest of the kernel still runs, and a second
- * kernel (started while the first one ends) waits for the peers' row patches and
- * writes the full rows [M, world*out_local] to `gathered`.  y_local [M, out_local]
- * still receives this rank's columns.  `fusion` (may be NULL) as in
- * bqq_forward_decode_fused; a residual is this rank's column slice [M, out_local]
- * and is added before the outputs are sent.  Same rules as bqq_forward_decode and
- * bqq_peer_gather; 16-bit outputs need an even P.  This is the sharded forward a
- * column-parallel wrapper of the reference module would need (the reference has no
- * multi-GPU path).
+ * bqq_forward_decode of a row-patch shard fused with the gather, in ONE launch:
+ * the decode kernel's epilogue stores every finished output row patch into the
+ * gather regions of all ranks while the rest of the kernel still runs, and a few
+ * additional CTAs of the same grid wait (bounded) for the peers' row patches and
+ * write the full rows [M, world*out_local] to `gathered`; the computing CTAs never
+ * wait for them.  y_local [M, out_local] still receives this rank's columns.
+ * `fusion` (may be NULL) as in bqq_forward_decode_fused; a residual is this rank's
+ * column slice [M, out_local] and is added before the outputs are sent.  Same
+ * rules as bqq_forward_decode and bqq_peer_gather; 16-bit outputs need an even P.
+ * This is the sharded forward a column-parallel wrapper of the reference module
+ * would need (the reference has no multi-GPU path).
  */
 int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
                                 void* y_local, int y_dtype, int64_t ldy, const BqqFusion* fusion,
