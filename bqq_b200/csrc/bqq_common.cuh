@@ -135,6 +135,21 @@ __device__ __forceinline__ uint2 peer_slot_load(const void* p) {
   return make_uint2((uint32_t)v, (uint32_t)(v >> 32));
 }
 
+// Roles of a kernel in a chain of programmatic dependent launches (every kernel of such a chain is launched with
+// the programmatic stream serialisation attribute; without the attribute the instructions do nothing).
+//   kPdlWaitFirst  needs what its predecessors wrote: waits for them to complete, then lets its successor start
+//   kPdlOverlap    independent of its predecessor: lets its successor start at once and runs beside its
+//                  predecessor; one CTA waits for the predecessor at the very end, so that "this grid has
+//                  completed" still implies "everything before it has completed" for whoever waits on it
+constexpr int kPdlNone = 0, kPdlWaitFirst = 1, kPdlOverlap = 2;
+__device__ __forceinline__ void pdl_enter(int mode) {
+  if (mode == kPdlWaitFirst) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (mode != kPdlNone) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_exit(int mode) {
+  if (mode == kPdlOverlap && blockIdx.x == 0 && blockIdx.y == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? BQQ_OK : BQQ_ERR_CUDA;
@@ -152,8 +167,9 @@ constexpr size_t kPeerCtrlBytes = 512;   // control words at the start of a peer
 
 int decode_launches(const BqqDims* dims, int M);   // kernels per decode call: 1 or 2
 size_t decode_counter_bytes();   // leading part of the decode workspace that must start zeroed
+// row patches [i0, i1) only (i1 < 0: all); pdl: role in a chain of programmatic dependent launches
 int reconstruct_launch(const BqqLayer* layer, void* W, void* W_lo, int w_dtype, float scale,
-                       const float* bound_parts, cudaStream_t stream);
+                       const float* bound_parts, cudaStream_t stream, int i0 = 0, int i1 = -1, int pdl = kPdlNone);
 int coef_bound_launch(const BqqLayer* layer, float* bound_parts, cudaStream_t stream);   // bound_parts zero on entry
 int prefill_launch(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx, void* y,
                    int y_dtype, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream);

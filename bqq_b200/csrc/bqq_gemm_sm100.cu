@@ -7,14 +7,21 @@
 // split into bf16 hi + lo the same way (passes hi*hi, hi*lo, lo*hi).  Replaces reconstruct_W_kernel + torch::mm of
 // the reference (neural_network_compression/src/bqq_cuda.cu:198-246, 367-383).
 //
-// GEMM kernel, one 128 x BN output tile per CTA (BN = 256, 128, 64 or 32), 6 warps:
-//   warp 0   TMA producer: 4-stage ring of {A 128x64, B BNx64} 16-bit tiles,
-//            128-byte swizzle, completion on mbarriers
-//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN,
-//            K=16 per instruction) and commits stage releases to mbarriers
+// GEMM kernel, one (128 MT) x BN output tile per CTA (BN = 256, 128, 64 or 32; MT = 1 or 2 row
+// halves that share the B tile: with MT = 2 a k-block moves 64 KB for 256 x 256 outputs instead of
+// 48 KB for 128 x 256, a third less traffic from the L2 per product), 6 warps:
+//   warp 0   TMA producer: ring of {A (128 MT)x64, B BNx64} 16-bit tiles (4 stages, 3 for the
+//            256 x 256 tile), 128-byte swizzle, completion on mbarriers
+//   warp 1   allocates tensor memory (MT accumulators of BN columns); one lane issues tcgen05.mma
+//            (M=128, N=BN, K=16 per instruction) and commits stage releases to mbarriers
 //   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, scale, bias, convert, store
 // Every mbarrier wait is bounded by a clock budget; on expiry the kernel records
 // a status code in global memory, drains its copies and returns.
+//
+// The call is a chain of programmatic dependent launches over column panels of W (about one wave of
+// GEMM tiles each): bound, rebuild panel 0, stage x, then alternately multiply panel p and rebuild
+// panel p+1.  A GEMM waits for everything before it and then lets the next rebuild start at once, so the
+// rebuild of a panel (ALU work) runs beside the GEMM of the previous one (TMA and tensor pipe).
 #include <cuda.h>
 
 #include "bqq_async.cuh"
@@ -24,8 +31,8 @@ namespace bqq {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;          // 64 x 2 bytes = one 128-byte swizzle row
-constexpr int kStages = 4;
 constexpr int kGemmThreads = 192;
+__host__ __device__ constexpr int gemm_stages(int BN, int MT) { return (BN == 256 && MT == 2) ? 3 : 4; }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -82,15 +89,19 @@ struct GemmParams {
   int a_sel[3];              // per pass: 0 = first activation map, 1 = second (low half of fp32 x)
   int b_row[3];              // per pass: row offset into the stacked W map (0 = hi / only part, N = lo part)
   uint32_t idesc;
+  int n_tile0;               // first BN-column tile of this launch (column panels of W are multiplied one after the other)
 };
 
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1,
                 const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t gsm[];
-  constexpr uint32_t kABytes = kBM * kBK * 2;
+  constexpr int kStages = gemm_stages(BN, MT);
+  constexpr uint32_t kAHalf = kBM * kBK * 2;              // one 128-row half of the A tile
+  constexpr uint32_t kABytes = MT * kAHalf;
   constexpr uint32_t kBBytes = BN * kBK * 2;
+  constexpr uint32_t kCols = BN * MT;                     // tensor-memory columns: MT accumulators side by side
   // 1024-byte aligned tiles (required by the 128-byte swizzle)
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gsm) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = base;
@@ -101,10 +112,13 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
   volatile uint32_t* failed = tmem_slot + 1;
 
+  // everything before this launch (the rebuilt panel of W, the staged x) has to be complete; the next kernel of the
+  // stream (the rebuild of the following panel) may start now and run beside this one
+  pdl_enter(kPdlWaitFirst);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * kBM;
+  const int n0 = (blockIdx.x + p.n_tile0) * BN;
+  const int m0 = blockIdx.y * (kBM * MT);
   const int kblocks = (p.K + kBK - 1) / kBK;
   const int iters = kblocks * p.passes;
 
@@ -115,7 +129,7 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
     mbar_init_fence();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -153,11 +167,14 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
         const uint32_t ph = (uint32_t)(it / kStages) & 1u;
         if (*failed || !mbar_wait(full_bar + s, ph)) { *failed = 1; ok = false; break; }
         tc_fence_after();
-        const uint64_t adesc = make_smem_desc(smem_u32(sA + s * kABytes));
         const uint64_t bdesc = make_smem_desc(smem_u32(sB + s * kBBytes));
 #pragma unroll
-        for (int k = 0; k < kBK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units per step
-          tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, p.idesc, (it | k) != 0 ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint64_t adesc = make_smem_desc(smem_u32(sA + s * kABytes + mt * kAHalf));
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units per step
+            tc_mma_f16(tmem_base + (uint32_t)(mt * BN), adesc + 2 * k, bdesc + 2 * k, p.idesc, (it | k) != 0 ? 1u : 0u);
+        }
         tc_commit(empty_bar + s);            // frees the stage when these MMAs have read it
       }
       tc_commit(acc_bar);                    // accumulator complete (or abandoned)
@@ -170,12 +187,14 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
     tc_fence_after();
     if (ok) {
       const float w_unscale = p.bound_parts ? 1.f / w_scale_from_bound(p.bound_parts, p.bound_mult) : 1.f;
-      const int m = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+      const int m = m0 + mt * kBM + quarter * 32 + lane;
       const float row_f = (p.row_unscale && m < p.M) ? p.row_unscale[m] : 1.f;
       const float inv_scale = w_unscale * row_f;
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
-        tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+        tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * BN + c * 32), v);
         tc_wait_ld();
         const int nb = n0 + c * 32;
         if (m < p.M && nb < p.N) {
@@ -216,13 +235,14 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
           }
         }
       }
+      }
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kCols) : "memory");
   }
   if (threadIdx.x == 0 && *failed) atomicExch(p.status, 1u);
 }
@@ -230,6 +250,7 @@ bqq_gemm_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constan
 // ---- x staging: any dtype / stride -> dense 16-bit rows (hi, lo for fp32) ----
 __global__ void stage_x_kernel(const void* __restrict__ x, int x_dtype, int64_t ldx, int M, int K, int Kp,
                                uint16_t* __restrict__ hi, uint16_t* __restrict__ lo) {
+  pdl_enter(kPdlOverlap);
   const size_t n = (size_t)M * Kp;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < n; t += (size_t)gridDim.x * blockDim.x) {
     const int k = (int)(t % Kp);
@@ -244,6 +265,7 @@ __global__ void stage_x_kernel(const void* __restrict__ x, int x_dtype, int64_t 
       hi[t] = k < K ? reinterpret_cast<const uint16_t*>(x)[m * ldx + k] : (uint16_t)0;
     }
   }
+  pdl_exit(kPdlOverlap);
 }
 
 // bf16 rows -> fp16 rows scaled by a per-row power of two (max |x| of the row maps to at most 2^14,
@@ -256,6 +278,7 @@ __global__ void __launch_bounds__(kStageThreads)
 stage_x_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int M, int K,
                            __half* __restrict__ out, float* __restrict__ row_unscale, int vec) {
   __shared__ float warp_max[kStageThreads / 32];
+  pdl_enter(kPdlOverlap);
   const int tid = threadIdx.x, lane = tid & 31;
   for (int m = blockIdx.x; m < M; m += gridDim.x) {
     const __nv_bfloat16* row = x + (size_t)m * ldx;
@@ -323,6 +346,7 @@ stage_x_bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int
     }
     if (tid == 0) row_unscale[m] = 1.f / scale;
   }
+  pdl_exit(kPdlOverlap);
 }
 
 // ---- host side -----------------------------------------------------------------
@@ -370,16 +394,43 @@ size_t prefill_workspace_bytes(const BqqDims* dims, int M) {
 }
 
 
-template <int BN>
-static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
-                       cudaStream_t st) {
-  const size_t smem = 1024 + (size_t)kStages * (kBM * kBK * 2 + BN * kBK * 2) + 256;
-  auto kern = bqq_gemm_kernel<BN>;
+static cudaLaunchAttribute pdl_attribute() {
+  cudaLaunchAttribute a;
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = 1;
+  return a;
+}
+
+// tiles [tile0, tile0 + ntiles) along N, all of M
+template <int BN, int MT>
+static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, GemmParams p, int tile0,
+                       int ntiles, cudaStream_t st) {
+  const size_t smem = 1024 + (size_t)gemm_stages(BN, MT) * (MT * kBM * kBK * 2 + BN * kBK * 2) + 256;
+  auto kern = bqq_gemm_kernel<BN, MT>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return BQQ_ERR_CUDA;
-  dim3 grid((p.N + BN - 1) / BN, (p.M + kBM - 1) / kBM);
-  kern<<<grid, kGemmThreads, smem, st>>>(a0, a1, b, p);
+  p.n_tile0 = tile0;
+  cudaLaunchAttribute attr[1] = {pdl_attribute()};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ntiles, (p.M + kBM * MT - 1) / (kBM * MT));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, a0, a1, b, p) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
+}
+
+static int launch_gemm_bn(int BN, int MT, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b,
+                          const GemmParams& p, int tile0, int ntiles, cudaStream_t st) {
+  if (MT == 2) return launch_gemm<256, 2>(a0, a1, b, p, tile0, ntiles, st);
+  switch (BN) {
+    case 256: return launch_gemm<256, 1>(a0, a1, b, p, tile0, ntiles, st);
+    case 128: return launch_gemm<128, 1>(a0, a1, b, p, tile0, ntiles, st);
+    case 64: return launch_gemm<64, 1>(a0, a1, b, p, tile0, ntiles, st);
+    default: return launch_gemm<32, 1>(a0, a1, b, p, tile0, ntiles, st);
+  }
 }
 
 int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t ldx, void* y, int y_dtype,
@@ -398,56 +449,43 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
 
   if (cudaMemsetAsync(status, 0, 32, st) != cudaSuccess) return BQQ_ERR_CUDA;   // status word and bound parts
 
-  // 1. dense W into scratch.  fp16 and bf16 activations use one fp16 W scaled by a power of two
-  //    (bf16 rows are re-staged as scaled fp16, exact); fp32 activations use the bf16 hi + lo pair.
   const bool f16 = x_dtype != BQQ_F32;
-  int rc;
-  if (f16) {
-    rc = coef_bound_launch(L, bound_parts, st);
-    if (rc) return rc;
-    rc = reconstruct_launch(L, W, nullptr, BQQ_F16, 1.f, bound_parts, st);
-  } else {
-    rc = reconstruct_launch(L, W, W + (size_t)N * K, BQQ_BF16, 1.f, nullptr, st);
-  }
-  if (rc) return rc;
-
-  // 2. x: fp16 is used in place when its pitch suits TMA; everything else is staged
-  const bool direct = x_dtype == BQQ_F16 && (ldx % 8) == 0 && ((uintptr_t)x & 15) == 0;
-  const void* a_ptr = x;
-  int64_t a_ld = ldx;
-  const float* row_unscale = nullptr;
-  if (x_dtype == BQQ_BF16) {
-    float* unscale = reinterpret_cast<float*>(xlo);          // the lo region is free on this path
-    const int vec = (K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
-    stage_x_bf16_to_f16_kernel<<<M, kStageThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx, M, K,
-                                                           reinterpret_cast<__half*>(xhi), unscale, vec);
-    rc = launch_status();
-    if (rc) return rc;
-    a_ptr = xhi;
-    a_ld = K;
-    row_unscale = unscale;
-  } else if (!direct) {
-    size_t n = (size_t)M * K;
-    int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    stage_x_kernel<<<blocks, 256, 0, st>>>(x, x_dtype, ldx, M, K, K, xhi, xlo);
-    rc = launch_status();
-    if (rc) return rc;
-    a_ptr = xhi;
-    a_ld = K;
-  }
   const bool split_x = x_dtype == BQQ_F32;
-
   // widest tile that still gives about one CTA per SM: small batches are bound by how many SMs stream W
   int BN = 32;
   for (int cand = 256; cand >= 64; cand >>= 1) {
     const long long ctas = (long long)((N + cand - 1) / cand) * ((M + kBM - 1) / kBM);
     if (ctas >= 118) { BN = cand; break; }
   }
+  // two row halves per CTA (256 x 256 outputs on one B tile) where that still gives about one CTA per SM
+  const int MT = (BN == 256 && (long long)((N + 255) / 256) * ((M + 2 * kBM - 1) / (2 * kBM)) >= 118) ? 2 : 1;
+  // Column panels of W of about one wave of GEMM tiles each (at most 4): the rebuild of panel p+1 runs beside the
+  // GEMM of panel p.  A panel border must not cut a row patch (the rebuild works on whole row patches).
+  const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + kBM * MT - 1) / (kBM * MT);
+  int panels = (int)(((long long)tiles_n * tiles_m + 74) / 148);
+  panels = panels < 1 ? 1 : (panels > 4 ? 4 : panels);
+  if (panels > tiles_n) panels = tiles_n;
+  if (BN % g.P != 0) panels = 1;
+  const int tiles_pp = (tiles_n + panels - 1) / panels;
+  panels = (tiles_n + tiles_pp - 1) / tiles_pp;
+  auto panel_rows = [&](int pnl, int* i0, int* i1) {           // row patches of panel pnl
+    const int c0 = pnl * tiles_pp * BN, c1 = std::min(N, (pnl + 1) * tiles_pp * BN);
+    *i0 = c0 / g.P;
+    *i1 = (c1 + g.P - 1) / g.P;
+  };
+
+  // x: fp16 is used in place when its pitch suits TMA; everything else is staged
+  const bool direct = x_dtype == BQQ_F16 && (ldx % 8) == 0 && ((uintptr_t)x & 15) == 0;
+  const void* a_ptr = direct ? x : (const void*)xhi;
+  const int64_t a_ld = direct ? ldx : (int64_t)K;
+  float* unscale = reinterpret_cast<float*>(xlo);            // the lo region is free when x has 16 bits
+  const float* row_unscale = x_dtype == BQQ_BF16 ? unscale : nullptr;
+
   CUtensorMap ma0, ma1, mb;
-  rc = make_map(&ma0, a_ptr, !f16, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, kBM);
+  int rc = make_map(&ma0, a_ptr, !f16, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, kBM * MT);
   if (rc) return rc;
   rc = make_map(&ma1, split_x ? (const void*)xlo : a_ptr, !f16, (uint64_t)M, (uint64_t)K,
-                split_x ? (uint64_t)K : (uint64_t)a_ld, kBM);
+                split_x ? (uint64_t)K : (uint64_t)a_ld, kBM * MT);
   if (rc) return rc;
   rc = make_map(&mb, W, !f16, (uint64_t)(f16 ? N : 2 * N), (uint64_t)K, (uint64_t)K, (uint32_t)BN);
   if (rc) return rc;
@@ -458,6 +496,7 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   p.row_unscale = row_unscale;
   p.ldy = ldy; p.y_dtype = y_dtype; p.bias_dtype = L->bias_dtype;
   p.M = M; p.N = N; p.K = K;
+  p.n_tile0 = 0;
   for (int i = 0; i < 3; ++i) { p.a_sel[i] = 0; p.b_row[i] = 0; }
   if (f16) {
     p.passes = 1;
@@ -467,12 +506,63 @@ int prefill_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t
   // instruction descriptor: fp32 accumulate, A and B in the same 16-bit format, both K-major
   const uint32_t fmt = f16 ? 0u : 1u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-  switch (BN) {
-    case 256: return launch_gemm<256>(ma0, ma1, mb, p, st);
-    case 128: return launch_gemm<128>(ma0, ma1, mb, p, st);
-    case 64: return launch_gemm<64>(ma0, ma1, mb, p, st);
-    default: return launch_gemm<32>(ma0, ma1, mb, p, st);
+
+  // 1. (16-bit x) bound on |W| for the power-of-two scale of the fp16 weight.  fp16 and bf16 activations use one
+  //    fp16 W (bf16 rows are re-staged as scaled fp16, exact); fp32 activations use the bf16 hi + lo pair.
+  if (f16) {
+    rc = coef_bound_launch(L, bound_parts, st);
+    if (rc) return rc;
   }
+  // 2. panel 0 of W: waits for the bound (and for whatever preceded this call in the stream)
+  auto rebuild = [&](int pnl, int pdl) {
+    int i0, i1;
+    panel_rows(pnl, &i0, &i1);
+    return f16 ? reconstruct_launch(L, W, nullptr, BQQ_F16, 1.f, bound_parts, st, i0, i1, pdl)
+               : reconstruct_launch(L, W, W + (size_t)N * K, BQQ_BF16, 1.f, nullptr, st, i0, i1, pdl);
+  };
+  rc = rebuild(0, kPdlWaitFirst);
+  if (rc) return rc;
+  // 3. x staging, beside the rebuild of panel 0
+  if (x_dtype == BQQ_BF16) {
+    const int vec = (K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
+    cudaLaunchAttribute attr[1] = {pdl_attribute()};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M);
+    cfg.blockDim = dim3(kStageThreads);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, stage_x_bf16_to_f16_kernel, reinterpret_cast<const __nv_bfloat16*>(x), ldx, M, K,
+                           reinterpret_cast<__half*>(xhi), unscale, vec) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
+  } else if (!direct) {
+    size_t n = (size_t)M * K;
+    int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    cudaLaunchAttribute attr[1] = {pdl_attribute()};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, stage_x_kernel, x, x_dtype, ldx, M, K, K, xhi, xlo) != cudaSuccess) {
+      cudaGetLastError();
+      return BQQ_ERR_CUDA;
+    }
+  }
+  rc = launch_status();
+  if (rc) return rc;
+  // 4. alternately: multiply panel p (waits for everything before it, then lets its successor start), rebuild
+  //    panel p+1 beside it (its last CTA waits for that GEMM, so the next GEMM's wait covers both)
+  for (int pnl = 0; pnl < panels; ++pnl) {
+    const int tile0 = pnl * tiles_pp, ntiles = std::min(tiles_pp, tiles_n - tile0);
+    rc = launch_gemm_bn(BN, MT, ma0, ma1, mb, p, tile0, ntiles, st);
+    if (rc) return rc;
+    if (pnl + 1 < panels) {
+      rc = rebuild(pnl + 1, kPdlOverlap);
+      if (rc) return rc;
+    }
+  }
+  return BQQ_OK;
 }
 
 }  // namespace bqq

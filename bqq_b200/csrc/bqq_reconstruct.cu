@@ -30,6 +30,9 @@ struct ReconParams {
   int pairs;                   // 1: two neighbouring entries of a row may be stored as one aligned word
   Geom g;
   int tasks_per_row;           // cw * PT * QT: 32x32 blocks of one row patch
+  int i0, i1;                  // row patches [i0, i1) are rebuilt
+  // How the launch takes part in a chain of programmatic dependent launches (kPdl* in bqq_common.cuh)
+  int pdl;
 };
 
 // element type of W as a compile-time choice
@@ -135,6 +138,7 @@ bqq_reconstruct_kernel(const ReconParams p) {
   const Geom& g = p.g;
   const int lane = threadIdx.x & 31;
   const int g8 = lane >> 2, t4 = lane & 3;
+  pdl_enter(p.pdl);
   const float scale = p.bound_parts ? p.scale * w_scale_from_bound(p.bound_parts, (float)(g.bw * g.r)) : p.scale;
   const float s_core = scale / (kBitValue * kBitValue), s_sum = scale / kBitValue;
   const size_t ldw = (size_t)g.cw * g.Q;
@@ -155,7 +159,8 @@ bqq_reconstruct_kernel(const ReconParams p) {
   unsigned tj = blockIdx.x * kReconWarps + (threadIdx.x >> 5);
   int i = (int)(tj / tpr);
   tj -= (unsigned)i * tpr;
-  bool have = i < g.rw;
+  i += p.i0;
+  bool have = i < p.i1;
   ReconTask cur = recon_locate<RT>(p, have ? i : 0, have ? tj : 0u, lane, zsrc);
   uint32_t yw_n = 0u, zw_n = 0u;
   float ca_n = 0.f, cb_n = 0.f, cc_n = 0.f, d_n = 0.f;
@@ -176,7 +181,7 @@ bqq_reconstruct_kernel(const ReconParams p) {
       ni += (int)k;
       ntj -= k * tpr;
     }
-    const bool have_next = ni < g.rw;
+    const bool have_next = ni < p.i1;
     const ReconTask nxt = have_next ? recon_locate<RT>(p, ni, ntj, lane, zsrc) : cur;
 
     float acc[2][4][4];          // [16-row tile][8-column tile][fragment entry]
@@ -304,26 +309,42 @@ bqq_reconstruct_kernel(const ReconParams p) {
     tj = ntj;
     have = have_next;
   }
+  pdl_exit(p.pdl);
+}
+
+template <typename K>
+static int recon_launch_one(K kern, const ReconParams& p, dim3 blocks, cudaStream_t st) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = blocks;
+  cfg.blockDim = dim3(kReconWarps * 32);
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl != kPdlNone ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
+  return launch_status();
 }
 
 template <int RT>
-static void reconstruct_dispatch(const ReconParams& p, dim3 blocks, cudaStream_t st) {
-  const int threads = kReconWarps * 32;
+static int reconstruct_dispatch(const ReconParams& p, dim3 blocks, cudaStream_t st) {
   const bool lo = p.W_lo != nullptr;
-  if (p.w_dtype == BQQ_F32) bqq_reconstruct_kernel<RT, BQQ_F32, false><<<blocks, threads, 0, st>>>(p);
-  else if (p.w_dtype == BQQ_BF16) {
-    if (lo) bqq_reconstruct_kernel<RT, BQQ_BF16, true><<<blocks, threads, 0, st>>>(p);
-    else bqq_reconstruct_kernel<RT, BQQ_BF16, false><<<blocks, threads, 0, st>>>(p);
-  } else {
-    if (lo) bqq_reconstruct_kernel<RT, BQQ_F16, true><<<blocks, threads, 0, st>>>(p);
-    else bqq_reconstruct_kernel<RT, BQQ_F16, false><<<blocks, threads, 0, st>>>(p);
-  }
+  if (p.w_dtype == BQQ_F32) return recon_launch_one(bqq_reconstruct_kernel<RT, BQQ_F32, false>, p, blocks, st);
+  if (p.w_dtype == BQQ_BF16)
+    return lo ? recon_launch_one(bqq_reconstruct_kernel<RT, BQQ_BF16, true>, p, blocks, st)
+              : recon_launch_one(bqq_reconstruct_kernel<RT, BQQ_BF16, false>, p, blocks, st);
+  return lo ? recon_launch_one(bqq_reconstruct_kernel<RT, BQQ_F16, true>, p, blocks, st)
+            : recon_launch_one(bqq_reconstruct_kernel<RT, BQQ_F16, false>, p, blocks, st);
 }
 
 int reconstruct_launch(const BqqLayer* L, void* W, void* W_lo, int w_dtype, float scale, const float* bound_parts,
-                       cudaStream_t st) {
+                       cudaStream_t st, int i0, int i1, int pdl) {
   ReconParams p;
   p.g = Geom(L->dims);
+  p.i0 = i0;
+  p.i1 = i1 < 0 ? p.g.rw : i1;
+  p.pdl = pdl;
   p.zp = L->zplanes; p.yp = L->yplanes;
   p.a = L->a; p.b = L->b; p.c = L->c; p.d = L->d; p.coef_dtype = L->coef_dtype;
   p.W = W; p.W_lo = W_lo; p.scale = scale; p.bound_parts = bound_parts; p.w_dtype = w_dtype;
@@ -331,17 +352,18 @@ int reconstruct_launch(const BqqLayer* L, void* W, void* W_lo, int w_dtype, floa
   const uintptr_t pair_mask = 2 * (uintptr_t)dtype_size(w_dtype) - 1;
   p.pairs = (p.g.Q % 2 == 0 && ((uintptr_t)W & pair_mask) == 0 && ((uintptr_t)W_lo & pair_mask) == 0) ? 1 : 0;
   // resident warps walk the blocks: 4 CTAs per SM on 148 SMs
-  const long long tasks = (long long)p.tasks_per_row * p.g.rw;
+  const long long tasks = (long long)p.tasks_per_row * (p.i1 - p.i0);
+  if (tasks <= 0) return BQQ_OK;
   const dim3 blocks((unsigned)std::min<long long>((tasks + kReconWarps - 1) / kReconWarps, 148LL * 4));
   if (w_dtype == BQQ_F32 && W_lo) return BQQ_ERR_UNSUPPORTED;     // a second part only exists for 16-bit types
-  if (p.g.RT == 1) reconstruct_dispatch<1>(p, blocks, st);
-  else reconstruct_dispatch<2>(p, blocks, st);
-  return launch_status();
+  if (p.g.RT == 1) return reconstruct_dispatch<1>(p, blocks, st);
+  return reconstruct_dispatch<2>(p, blocks, st);
 }
 
 // bound_parts[0] = max(|a|+|b|+|c|), bound_parts[1] = max|d| (both must be zero on entry: the caller clears them)
 __global__ void coef_bound_kernel(const void* a, const void* b, const void* c, const void* d, int dt, size_t nabc,
                                   size_t nd, float* bound_parts) {
+  pdl_enter(kPdlWaitFirst);          // the bound words were cleared by a memset node: nothing to overlap with
   float m0 = 0.f, m1 = 0.f;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < nabc; t += (size_t)gridDim.x * blockDim.x)
     m0 = fmaxf(m0, fabsf(load_as_float(a, t, dt)) + fabsf(load_as_float(b, t, dt)) + fabsf(load_as_float(c, t, dt)));

@@ -107,6 +107,21 @@ def test_prefill_every_tile_width(M):
     assert O.max_rel_err(y32.cpu().numpy(), oracle_forward_t(Y, Z, A, bias, X)) < TOL
 
 
+@pytest.mark.parametrize('M,rw', [(512, 896), (2048, 160)])
+def test_prefill_column_panels(M, rw):
+    """Enough GEMM tiles for several waves: W is rebuilt and multiplied in column panels (the rebuild of a panel runs
+    beside the GEMM of the previous one), with two row halves per CTA.  Every output is checked."""
+    from bqq_b200.bqq_modules import BinaryQuadratic
+    Y, Z, A, bias, X = synth_layer(2, rw, 8, 32, 32, 32, M, seed=rw + M, x_dtype=torch.bfloat16, bias=True)
+    bq = BinaryQuadratic(Y.float(), Z.float(), A, bias=bias).cuda()
+    ref = oracle_forward_t(Y, Z, A, bias, X)
+    for _ in range(2):                                   # twice: the workspace is reused
+        y = _run(bq, X.cuda())
+        assert O.max_rel_err(y.float().cpu().numpy(), ref) < TOL + 2 ** -8
+    y32 = _run(bq, X.float().cuda())
+    assert O.max_rel_err(y32.cpu().numpy(), ref) < TOL
+
+
 def test_prefill_fp32_output_tolerance():
     """Config-3-like contraction (K = 4096) with fp32 outputs so only compute error remains."""
     from bqq_b200.bqq_modules import BinaryQuadratic
