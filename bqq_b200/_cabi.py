@@ -46,7 +46,8 @@ PRO_NONE, PRO_RMSNORM, PRO_SWIGLU = 0, 1, 2
 
 class BqqFusion(C.Structure):
     _fields_ = [('prologue', C.c_int32), ('norm_dtype', C.c_int32), ('norm_weight', C.c_void_p), ('eps', C.c_float),
-                ('residual_dtype', C.c_int32), ('residual', C.c_void_p), ('ld_residual', C.c_int64)]
+                ('residual_dtype', C.c_int32), ('residual', C.c_void_p), ('ld_residual', C.c_int64),
+                ('out_segments', C.c_int32)]
 
 
 MAX_PEERS = 8

@@ -297,7 +297,7 @@ class _BqqForwardMixin:
         return y.reshape(*X.shape[:-1], out_f)
 
     def forward_gathered(self, X, peer, out=None, rms_weight=None, eps: float = 1e-5, swiglu: bool = False,
-                         residual=None):
+                         residual=None, out_segments: int = 1):
         """Forward of a row-patch shard with the column gather built in: every rank calls it on its
         shard with the full activation X [..., in] and gets the full output [..., world*out_local]
         (columns in rank order).  `peer` is a bqq_b200.peer.PeerGatherGroup of the ranks.
@@ -305,7 +305,9 @@ class _BqqForwardMixin:
         Up to 16 rows the decode kernel itself stores each finished row patch into the peers' gather
         regions (bqq_forward_decode_gathered); larger batches run the forward and then the gather kernel.
         rms_weight / swiglu / residual as in forward_fused; `residual` is the full [..., world*out_local]
-        tensor, of which this rank adds its own columns before sending."""
+        tensor, of which this rank adds its own columns before sending.  `out_segments=2`: the local
+        output is two halves [h0 | h1] (a stacked gate / up layer) and the result is
+        [h0 of all ranks | h1 of all ranks], the [gate | up] rows a SwiGLU consumer expects."""
         self._check_inference_only(X)
         if X.dtype not in _DTYPE_CODE:
             raise RuntimeError(f'bqq_b200: unsupported activation dtype {X.dtype} (fp32, bf16, fp16 only)')
@@ -328,11 +330,19 @@ class _BqqForwardMixin:
         fused = (0 < M <= _cabi.DECODE_MAX_M and (out_f * esize) % 4 == 0
                  and (esize == 4 or self.y_row % 2 == 0)
                  and M * out_f * peer.world * esize <= peer.max_bytes)
+        if out_segments not in (1, 2) or (out_segments == 2 and (out_f % 2 or residual is not None)):
+            raise RuntimeError('bqq_b200: out_segments must be 1 or 2 (2: even out_features, no residual)')
         if not fused:
             y_local = self.forward_fused(X, rms_weight=rms_weight, eps=eps, swiglu=swiglu,
                                          residual=None if res_local is None else res_local.contiguous())
+            if out_segments == 2:
+                h = out_f // 2
+                both = torch.cat([peer.gather(y_local[..., :h].contiguous()), peer.gather(y_local[..., h:].contiguous())],
+                                 dim=-1)
+                return both if out is None else out.copy_(both.reshape(out.shape))
             return peer.gather(y_local, out=out)
         fusion, keep = self._fusion(M, rms_weight, eps, swiglu, res_local)
+        fusion.out_segments = out_segments
         if out is None:
             out = torch.empty((M, peer.world * out_f), dtype=X.dtype, device=device)
         o2 = out.reshape(M, peer.world * out_f)

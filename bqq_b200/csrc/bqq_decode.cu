@@ -128,6 +128,7 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
   p.peer_out = nullptr;
   p.peer_ld_out = p.peer_wait = 0;
   p.ncompute = g.rw * (g.bw / pl.bpc) * pl.nchunks;
+  p.peer_seg_words = 0;
   if (peer) {
     const size_t es = dtype_size(y_dtype);
     if (((size_t)g.out_features() * es) % 4 || (es == 2 && (g.P & 1))) return BQQ_ERR_MISALIGNED;   // outputs travel as 32-bit words
@@ -136,6 +137,12 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
     p.peer_rank = peer->rank;
     p.peer_row_words = (int)((size_t)g.out_features() * es / 4);
     p.peer_half = peer_half_bytes(peer->gather_bytes);
+    if (fusion && fusion->out_segments == 2) {
+      if (p.peer_row_words % 2) return BQQ_ERR_MISALIGNED;
+      p.peer_seg_words = p.peer_row_words / 2;
+    } else if (fusion && fusion->out_segments > 2) {
+      return BQQ_ERR_UNSUPPORTED;
+    }
     // the receiving side runs in the same launch: a few CTAs that poll this rank's region and write the rows
     if (!gathered) return BQQ_ERR_NULL;
     if ((((size_t)ld_gathered * es) % 4) || ((uintptr_t)gathered & 3)) return BQQ_ERR_MISALIGNED;

@@ -114,6 +114,8 @@ struct DecodeParams {
   long long peer_ld_out;     // row pitch of peer_out in 32-bit words
   long long peer_wait;       // clock budget of one wait on a peer
   int ncompute;              // CTAs along x that compute (the rest receive)
+  int peer_seg_words;        // > 0: the local row is two halves of this many words, gathered as [half 0 of every rank |
+                             // half 1 of every rank] (a stacked gate / up layer whose consumer wants [gate | up])
   int coef_vec;            // 1: fp32 coefficients, cw % 4 == 0, 16-byte aligned -> 128-bit loads
 };
 
@@ -395,7 +397,12 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
   const unsigned count = *reinterpret_cast<const volatile unsigned*>(mine) + 1u;
   const unsigned seq = count | 0x80000000u;
   const size_t wcol = p.y_dtype == BQQ_F32 ? (size_t)o : (size_t)o >> 1;
-  const size_t slot = ((size_t)row * p.peer_world + p.peer_rank) * p.peer_row_words + wcol;
+  size_t col = (size_t)p.peer_rank * p.peer_row_words + wcol;            // rank-major columns
+  if (p.peer_seg_words) {
+    const size_t sw = (size_t)p.peer_seg_words, seg = wcol >= sw ? 1 : 0;
+    col = seg * p.peer_world * sw + p.peer_rank * sw + (wcol - seg * sw);
+  }
+  const size_t slot = (size_t)row * p.peer_world * p.peer_row_words + col;
   const size_t off = kPeerCtrlBytes + (count & 1u) * p.peer_half + slot * 8;
   for (int q = 0; q < p.peer_world; ++q)
     peer_slot_store(p.peer_regions[q] + off, word, seq);

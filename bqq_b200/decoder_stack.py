@@ -149,6 +149,12 @@ class DecoderLayer(nn.Module):
             gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)
             return self.down_proj.forward_fused(gu, swiglu=True, residual=x)
         x = self._proj_gathered(self.o_proj, att, x)                                        # gather 2
+        rows = x.numel() // x.shape[-1]
+        if rows <= 16 and self._fits(rows, 2 * (self.cfg.intermediate // self.world), x.element_size()):
+            # the [gate | up] rows of all ranks are gathered by the layer's own launch, SwiGLU is applied by
+            # down_proj as it reads them: no element-wise kernel, no separate gather
+            gu = self.gate_up_proj.forward_gathered(x, self.peer, rms_weight=self.norm2, eps=1e-5, out_segments=2)
+            return self.down_proj.forward_gathered(gu, self.peer, swiglu=True, residual=x)  # gathers 3 and 4
         gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)
         n = gu.shape[-1] // 2
         act = F.silu(gu[..., :n]) * gu[..., n:]

@@ -204,6 +204,10 @@ typedef struct BqqFusion {
   int32_t residual_dtype;
   const void* residual;
   int64_t ld_residual;         /* row pitch of residual in elements */
+  int32_t out_segments;        /* bqq_forward_decode_gathered only: 0 or 1 = the gathered row is the ranks'
+                                  rows side by side; 2 = every rank's row is two halves [h0 | h1] and the
+                                  gathered row is [h0 of all ranks | h1 of all ranks] (a stacked gate / up
+                                  layer whose consumer applies BQQ_PRO_SWIGLU to [gate | up]) */
 } BqqFusion;
 int bqq_forward_decode_fused(const BqqLayer* layer, const void* x, int x_dtype, int M, int64_t ldx,
                              void* y, int y_dtype, int64_t ldy, const BqqFusion* fusion,

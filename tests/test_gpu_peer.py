@@ -93,6 +93,19 @@ def _worker(rank, world, port, result_dir):
                 want = full.forward_fused(Xd, rms_weight=w, residual=h)
                 got = shard.forward_gathered(Xd, grp, rms_weight=w, residual=h)
                 assert torch.equal(got, want), (rank, 'fused', bw, rw, cw, M)
+        # a stacked [gate ; up] layer: every rank holds [gate rows of its slice ; up rows of its slice]; gathered in two
+        # segments the result is the unsharded layer's [gate | up] row
+        bw, rw, cw = 2, 8 * world, 6
+        Y, Z, A, _, X = synth_layer(bw, rw, cw, 32, 32, 32, 3, seed=47)
+        full = BinaryQuadratic(Y.float(), Z.float(), A).to(dev)
+        half, per = rw // 2, rw // 2 // world
+        idx = torch.cat([torch.arange(rank * per, (rank + 1) * per), half + torch.arange(rank * per, (rank + 1) * per)])
+        shard = BinaryQuadratic(Y[:, idx].float(), Z[:, idx].float(), A[:, idx]).to(dev)
+        Xd = X.to(torch.bfloat16).to(dev)
+        with torch.no_grad():
+            want = full(Xd)
+            got = shard.forward_gathered(Xd, grp, out_segments=2)
+            assert torch.equal(got, want), (rank, 'two segments')
         grp.status()
         grp.close()
         with open(os.path.join(result_dir, f'ok{rank}'), 'w') as f:
