@@ -411,7 +411,7 @@ __device__ __forceinline__ void peer_send(const DecodeParams& p, bool valid, int
 // Receiving CTAs of a gathered decode launch (blockIdx.x >= ncompute): poll every slot of this rank's region until
 // it carries the gather's sequence number (bounded), write the data words to the caller's tensor.  They run beside
 // the computing CTAs of the same launch, which never wait for them.
-static __device__ __noinline__ void peer_receive(const DecodeParams& p) {
+__device__ __forceinline__ void peer_receive(const DecodeParams& p) {
   __shared__ int s_giveup;
   // the output tensor may still be read by earlier kernels of the stream; later kernels need not wait for the polling
   asm volatile("griddepcontrol.wait;" ::: "memory");
