@@ -44,6 +44,9 @@ static DecodePlan make_decode_plan(const Geom& g, int M) {
   // 28672x4096 the latter).  Both routes add in the same order and give identical bits, so this one choice
   // may depend on the number of row patches.
   pl.bpc = (pl.variant == 0 && pl.NB == 1 && pl.nchunks == 1 && g.bw <= 4 && g.rw * g.bw * kDW <= 3072) ? g.bw : 1;
+  // a CTA of 16 warps is alone on its SM: with more row patches than SMs a second, mostly empty wave would follow
+  // (6144x2048 with 4 bit layers: 11.8 us); two CTAs of 8 warps per row patch fit three to an SM (9.3 us)
+  if (pl.bpc == 4 && g.rw > 148) pl.bpc = 2;
   pl.nparts = (g.bw / pl.bpc) * pl.nchunks;
   // CTAs that take all bit layers of a short layer also prepare the x digits themselves (one launch).  Measured:
   // letting the CTAs of chunked layers prepare their own chunk as well (no preparation kernel at all) is slower,
