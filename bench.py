@@ -481,55 +481,93 @@ def extra_large_layer(device, rank, world, peer_factory, stream):
             peer = peer_factory(28672 * 2)              # one gathered row of the widest output
         except RuntimeError:
             peer = None
+    checks = []
     for (o, i) in ((8192, 28672), (28672, 8192)):
-        layer = make_layer(o // world, i, 3, device, seed=50 + rank, group=64, rank=64, last_bit_scale=0.005)
-        drop_bool_factors(layer)
+        # enough distinct copies of the rank's shard to exceed the L2 between two uses of one copy
+        shard_bytes = alg_bytes(o // world, i, 3, group=64)
+        ncopies = max(2, int(300e6 // shard_bytes) + 1)
+        layers = []
+        for c in range(ncopies):
+            layer = make_layer(o // world, i, 3, device, seed=50 + rank + 16 * c, group=64, rank=64, last_bit_scale=0.005)
+            drop_bool_factors(layer)
+            layers.append(layer)
         torch.cuda.empty_cache()
-        flush = torch.empty(160 << 20, dtype=torch.uint8, device=device)
         for M in (1, 32):
             x = torch.randn(M, i, device=device, dtype=torch.bfloat16)
             gathered = torch.empty(M, o, device=device, dtype=torch.bfloat16)
+            by_peer = peer is not None and M <= 16
 
-            def fwd():
+            def fwd(layer):
                 with torch.no_grad():
                     if world == 1:
                         return layer(x)
-                    if peer is not None and M <= 16:
+                    if by_peer:
                         return layer.forward_gathered(x, peer, out=gathered)
                     from bqq_b200.sharded import gather_columns
                     return gather_columns(layer(x))
 
             with torch.cuda.stream(stream):
-                for _ in range(3):
-                    fwd()
+                for layer in layers:
+                    fwd(layer)
                 stream.synchronize()
-                times = []
-                for _ in range(10):
-                    flush.zero_()                           # L2 flush (a shard can be smaller than the L2)
+                if by_peer:
+                    # the rows gathered by peer stores against a library all-gather of the shards' own outputs
+                    from bqq_b200.sharded import gather_columns
+                    with torch.no_grad():
+                        want = gather_columns(layers[0](x))
+                        got = layers[0].forward_gathered(x, peer, out=gathered)
+                    stream.synchronize()
+                    checks.append(bool(torch.equal(want, got)))
+                if world == 1 or by_peer:
+                    # one graph over all copies, replayed: the ranks stay in step through the gathers themselves
                     if world > 1:
                         dist.barrier()
-                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        for layer in layers:
+                            fwd(layer)
+                    for _ in range(3):
+                        graph.replay()
+                    stream.synchronize()
+                    reps = 10
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record(stream)
-                    fwd()
+                    for _ in range(reps):
+                        graph.replay()
                     e1.record(stream)
                     stream.synchronize()
-                    times.append(e0.elapsed_time(e1))
-            us = median(times) * 1e3
+                    us = e0.elapsed_time(e1) * 1e3 / (reps * ncopies)
+                    graph.reset()
+                    how = f'graph replay over {ncopies} copies of the shard (> L2)'
+                else:
+                    times = []
+                    for n in range(10):
+                        dist.barrier()
+                        torch.cuda.synchronize()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        fwd(layers[n % ncopies])
+                        e1.record(stream)
+                        stream.synchronize()
+                        times.append(e0.elapsed_time(e1))
+                    us = median(times) * 1e3
+                    how = f'eager launches after a barrier, copies of the shard in rotation ({ncopies}, > L2)'
             if world > 1:
                 t = torch.tensor([us], device=device, dtype=torch.float64)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 us = float(t.item())
             nbytes = alg_bytes(o, i, 3, M=M, group=64)
             out[f'{o}x{i}_m{M}'] = {'us': us, 'GB/s': nbytes / us / 1e3,
-                                    'gather': 'none' if world == 1 else ('peer stores' if peer is not None and M <= 16 else 'nccl')}
-        del layer, flush
+                                    'gather': 'none' if world == 1 else ('peer stores' if by_peer else 'nccl'),
+                                    'timing': how}
+        del layers, layer
         torch.cuda.empty_cache()
     if peer is not None:
         peer.status()
         peer.close()
-    out['note'] = ('whole-layer algorithmic bytes / max-over-ranks time of one forward incl. the gather; '
-                   'L2 flushed between timed forwards; eager launches (no graph)')
+    out['note'] = 'whole-layer algorithmic bytes / max-over-ranks time of one forward incl. the gather'
+    if checks:
+        out['gather_check'] = 'exact' if all(checks) else 'MISMATCH'
     return out
 
 
