@@ -639,6 +639,25 @@ def extra_stack(device, rank, world, peer_factory, new_tokens=128, prompt=512, b
 # headline
 # ---------------------------------------------------------------------------------------------------
 
+def run_rates(args):
+    """Issue rates of the candidate instructions (bqq_instruction_rate), one JSON line."""
+    import ctypes
+    import torch
+    from bqq_b200 import _cabi
+    torch.cuda.set_device(0)
+    names = ['mma.sync m16n8k32 u8*s8', 'mma.sync m16n8k16 f16', 'mma.sync m16n8k32 e4m3', 'mma.sync m16n8k64 u4*s4',
+             'mma.sync m16n8k256 b1 and.popc', 'lop3', 'add.f32', 'mad.lo.u32', 'popc', 'shfl']
+    out = {}
+    for kind, name in enumerate(names):
+        v = ctypes.c_double()
+        rc = _cabi.lib.bqq_instruction_rate(kind, 4096, ctypes.byref(v), None)
+        out[name] = round(v.value, 3) if rc == 0 else _cabi.strerror(rc)
+        print(f'{name:34s} {out[name]}', file=sys.stderr, flush=True)
+    print(json.dumps({'workload': 'rates', 'unit': 'warp-instructions per SM and clock (nominal SM clock)', 'rates': out}),
+          flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -647,7 +666,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='headline sweep only')
-    ap.add_argument('--workload', default='decode_sweep_b1', choices=['decode_sweep_b1', 'layer', 'shapes'])
+    ap.add_argument('--workload', default='decode_sweep_b1', choices=['decode_sweep_b1', 'layer', 'shapes', 'rates'])
     ap.add_argument('--out', type=int, default=4096)
     ap.add_argument('--in', dest='inp', type=int, default=14336)
     ap.add_argument('--bits', type=int, default=4)
@@ -665,6 +684,8 @@ def main():
         return run_layer(args)
     if args.workload == 'shapes':
         return run_shapes(args)
+    if args.workload == 'rates':
+        return run_rates(args)
 
     import torch
     import torch.distributed as dist

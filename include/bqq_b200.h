@@ -234,6 +234,18 @@ int bqq_prefill_status(const void* workspace, void* stream);
 int bqq_decode_launches(const BqqDims* dims, int M);
 
 /*
+ * Diagnostic: issue rate of one instruction kind on the current device, in
+ * warp-instructions per SM and clock (at the device's nominal SM clock), measured
+ * with CUDA events over one launch of `iters` rounds per warp on 32 warps per SM.
+ * kind: 0 mma.sync m16n8k32 u8*s8, 1 m16n8k16 f16, 2 m16n8k32 e4m3, 3 m16n8k64
+ * u4*s4, 4 m16n8k256 b1 and.popc, 5 lop3, 6 add.f32, 7 mad.lo.u32, 8 popc,
+ * 9 shfl.  The decode kernel's operand format (bytes masked out of the plane
+ * words for int8 MMAs) was chosen from these rates; `bench.py --workload rates`
+ * prints them.  Synchronises `stream`.  The reference has no counterpart.
+ */
+int bqq_instruction_rate(int kind, int iters, double* warp_inst_per_clk_per_sm, void* stream);
+
+/*
  * bqq_forward with HOST activations and outputs: copies x [M, ldx] from host
  * memory into the workspace, runs bqq_forward on the stream and copies y back to
  * host memory, all asynchronously on `stream` (use pinned host buffers; with
