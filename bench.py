@@ -623,6 +623,8 @@ def extra_stack(device, rank, world, peer_factory, new_tokens=128, prompt=512, b
            'layers': cfg.layers, 'scaling': 'strong', 'prompt': prompt, 'new_tokens': new_tokens,
            'prefill_ms': best_prefill, 'bqq_bytes_per_token_per_gpu': model.bqq_bytes_per_token(),
            'gathers': 'none' if world == 1 else 'peer stores', 'lm_head': 'dense bf16, included',
+           'attention': 'decode steps: bqq_attention_decode of this library (rotary embedding, cache append and '
+                        'attention in one launch); prefill: flash_attn library call',
            'coefficients': 'N(0, 0.02/sqrt(in/4096)) for a, 0.05 of that for b, c, d (keeps activations finite '
                            'through 32 random layers; speed does not depend on the values)'}
     graph.reset()

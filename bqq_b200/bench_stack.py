@@ -36,6 +36,11 @@ def main():
     ap.add_argument('--new', type=int, default=128)
     ap.add_argument('--repeats', type=int, default=3)
     ap.add_argument('--nccl-gathers', action='store_true', help='gather with the process group instead of peer stores')
+    ap.add_argument('--library-attention', action='store_true',
+                    help='decode steps use flash_attn (or torch ops) instead of the attention kernel of this package')
+    ap.add_argument('--mark-one-step', action='store_true',
+                    help='after the timed runs, replay one decode step between cudaProfilerStart/Stop (for a profiler '
+                         'started with capture off: the launch list of exactly one step)')
     args = ap.parse_args()
 
     rank = int(os.environ.get('RANK', '0'))
@@ -48,7 +53,7 @@ def main():
 
     cfg = StackConfig(layers=args.layers, hidden=args.hidden, intermediate=args.intermediate, heads=args.heads,
                       kv_heads=args.kv_heads, vocab=args.vocab, bit_width=args.bits, group=args.group,
-                      max_seq=args.prompt + args.new)
+                      max_seq=args.prompt + args.new, own_attention=not args.library_attention)
     peer = None
     if world > 1 and not args.nccl_gathers:
         from .peer import PeerGatherGroup
@@ -89,6 +94,13 @@ def main():
             pre, dec = e0.elapsed_time(e1), e1.elapsed_time(e2)
             best_prefill = pre if best_prefill is None else min(best_prefill, pre)
             best_decode = dec if best_decode is None else min(best_decode, dec)
+    if args.mark_one_step:
+        with torch.cuda.stream(stream):
+            stream.synchronize()
+            torch.cuda.profiler.start()
+            graph.replay()
+            stream.synchronize()
+            torch.cuda.profiler.stop()
     if world > 1:
         t = torch.tensor([best_decode, best_prefill], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

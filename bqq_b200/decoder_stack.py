@@ -9,9 +9,10 @@ lm_head kept dense because the reference's replacement skips names containing 'h
 decode loop (lm/benchmark_inference.py:24-85): random binary factors, greedy decode with a
 KV cache.
 
-Only the BinaryQuadratic layers are the product here; rotary embedding, cache append and attention
-are one flash_attn library call where that package is present (plain torch ops otherwise), the dense
-lm_head is a torch matmul (plumbing).  With world > 1 the layers are
+Only the BinaryQuadratic layers are the product here.  In a decode step rotary embedding, cache append and
+attention are one kernel of this library between two projections (bqq_attention_decode, part of the same chain of
+programmatic dependent launches); the prefill uses one flash_attn library call where that package is present
+(plain torch ops otherwise); the dense lm_head is a torch matmul (plumbing).  With world > 1 the layers are
 column-parallel (bqq_b200/sharded.py): q/k/v (one stacked layer) are sharded by heads so attention
 runs on local heads, gate/up (one stacked layer) share one sharding so SwiGLU is local, o_proj and down_proj are row-patch
 sharded; four gathers per layer, all without reductions.  With a PeerGatherGroup the gathers are the
@@ -32,6 +33,36 @@ import torch.nn.functional as F
 from .bqq_modules import BinaryQuadratic
 from .sharded import gather_columns
 
+_ATT_WS: dict = {}
+
+
+def attention_decode(qkv, k_cache, v_cache, cos, sin, lens, heads, kv_heads):
+    """Attention of one new token per sequence with this library's kernel (bqq_attention_decode): rotary embedding
+    of q and k at position lens[b], append of k and v to the caches, softmax(q K^T / sqrt(d)) V over the cached
+    rows.  qkv [B, 1, heads + 2 kv_heads, 128] bf16, caches [B, max_seq, kv_heads, 128]; returns [B, 1, heads, 128].
+    Returns None where the kernel does not apply (other types or head sizes), so the caller can take another route."""
+    from . import _cabi
+    B, T, H, hd = qkv.shape
+    if (T != 1 or hd != 128 or qkv.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or heads // kv_heads > 16
+            or not qkv.is_contiguous() or k_cache.stride(1) != kv_heads * hd or k_cache.stride(2) != hd
+            or v_cache.stride() != k_cache.stride() or not cos.is_contiguous() or not sin.is_contiguous()
+            or cos.dtype != torch.bfloat16 or lens.dtype != torch.int32):
+        return None
+    need = _cabi.lib.bqq_attention_decode_workspace_bytes(B, heads, kv_heads)
+    stream = torch.cuda.current_stream(qkv.device)
+    key = (qkv.device, stream.cuda_stream, B, heads, kv_heads)
+    ws = _ATT_WS.get(key)
+    if ws is None:
+        ws = _ATT_WS[key] = torch.zeros(need, dtype=torch.uint8, device=qkv.device)
+    out = torch.empty((B, 1, heads, hd), dtype=qkv.dtype, device=qkv.device)
+    _cabi.check(_cabi.lib.bqq_attention_decode(qkv.data_ptr(), qkv.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                                               k_cache.stride(0), k_cache.shape[1], cos.data_ptr(), sin.data_ptr(),
+                                               lens.data_ptr(), B, heads, kv_heads, hd, _cabi.BF16, out.data_ptr(),
+                                               out.stride(0), ws.data_ptr(), ws.numel(), stream.cuda_stream),
+                'bqq_attention_decode')
+    return out
+
+
 try:        # library kernel for the attention part of the harness: rotary embedding, cache append and attention in one launch
     from flash_attn import flash_attn_with_kvcache as _flash_kvcache
 except Exception:                                   # not installed: the plain torch ops below do the same
@@ -50,6 +81,7 @@ class StackConfig:
     group: int = 32            # P = Q = r
     max_seq: int = 1024
     rope_theta: float = 500000.0
+    own_attention: bool = True     # decode steps: this library's attention kernel (else flash_attn / torch ops)
 
     @property
     def head_dim(self) -> int:
@@ -122,7 +154,12 @@ class DecoderLayer(nn.Module):
         lh, lkv = self.local_heads, self.local_kv
         # normalisation, SwiGLU and residual adds are folded into the layers' kernels (forward_fused)
         qkv = self.qkv_proj.forward_fused(x, rms_weight=self.norm1, eps=1e-5).view(B, T, lh + 2 * lkv, hd)
-        if fa is not None and _flash_kvcache is not None and x.dtype in (torch.bfloat16, torch.float16):
+        att = None
+        if fa is not None and T == 1 and cfg.own_attention:
+            att = attention_decode(qkv, k_cache, v_cache, fa[0], fa[1], fa[2], lh, lkv)
+        if att is not None:
+            pass
+        elif fa is not None and _flash_kvcache is not None and x.dtype in (torch.bfloat16, torch.float16):
             cos, sin, lens = fa
             att = _flash_kvcache(qkv[:, :, :lh], k_cache, v_cache, k=qkv[:, :, lh:lh + lkv], v=qkv[:, :, lh + lkv:],
                                  rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens, causal=True,
@@ -211,7 +248,14 @@ class DecoderStack(nn.Module):
                 logits = self.peer.gather(logits)
             else:
                 logits = gather_columns(logits)
-        return logits.argmax(dim=-1)
+        # argmax in two stages (a single reduction over 128256 columns runs in one CTA): per chunk, then over the chunks
+        V = logits.shape[-1]
+        c = next((c for c in range(min(V, 1024), 63, -1) if V % c == 0), 0)
+        if c == 0:
+            return logits.argmax(dim=-1)
+        vals, idx = logits.reshape(-1, V // c, c).max(dim=2)
+        best = vals.argmax(dim=1, keepdim=True)
+        return (best * c + idx.gather(1, best)).squeeze(1)
 
     @torch.no_grad()
     def prefill(self, ids, cache):
@@ -229,9 +273,13 @@ class DecoderStack(nn.Module):
         """One greedy decode step with static shapes (CUDA-graph capturable).
         ids [B] int64, pos 1-element int64 device tensor; returns next ids [B]."""
         x = self.embed[ids].unsqueeze(1)
-        rot = self.rot.index_select(0, pos)
-        mask = (torch.arange(self.cfg.max_seq, device=self.device) <= pos).view(1, 1, 1, -1)
-        fa = (self.cos, self.sin, pos.to(torch.int32).expand(ids.shape[0]).contiguous()) if self.use_flash else None
+        fa = ((self.cos, self.sin, pos.to(torch.int32).expand(ids.shape[0]).contiguous())
+              if (self.use_flash or self.cfg.own_attention) else None)
+        needs_torch_route = fa is None or (not self.use_flash and (
+            x.dtype != torch.bfloat16 or self.cfg.head_dim != 128 or self.cfg.heads // self.cfg.kv_heads > 16))
+        rot = self.rot.index_select(0, pos) if needs_torch_route else None
+        mask = ((torch.arange(self.cfg.max_seq, device=self.device) <= pos).view(1, 1, 1, -1)
+                if needs_torch_route else None)
         for li, layer in enumerate(self.layers):
             x = layer(x, cache[li, 0], cache[li, 1], pos, rot, mask, fa=fa)
         return self._head(x[:, -1])

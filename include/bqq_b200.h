@@ -234,6 +234,32 @@ int bqq_prefill_status(const void* workspace, void* stream);
 int bqq_decode_launches(const BqqDims* dims, int M);
 
 /*
+ * Glue for decoder blocks built from these layers (no counterpart in the
+ * reference, whose host models call torch's scaled_dot_product_attention): the
+ * attention of ONE new token per sequence, in one launch.  qkv [B][heads +
+ * 2 kv_heads][head_dim] is the row the stacked q/k/v projection produced (ld_qkv
+ * elements between sequences); the new q and k heads get the rotary embedding of
+ * position lens[b] (pairs (x[2i], x[2i+1]) rotated by cos/sin_table[lens[b]][i],
+ * tables [max_seq][head_dim/2]), k and v are written to row lens[b] of the caches
+ * [B][max_seq][kv_heads][head_dim] (ld_cache elements between sequences), and out
+ * [B][heads][head_dim] (ld_out between sequences) receives softmax(q K^T /
+ * sqrt(head_dim)) V over rows 0..lens[b] for every query head (query head h reads
+ * kv head h / (heads / kv_heads)).  The key range is split over CTAs and combined
+ * in a fixed order, so results are reproducible.  lens is device memory, read by
+ * the kernel (the call can be captured in a CUDA graph); sequences with lens[b]
+ * outside [0, max_seq) are skipped.  bf16 only (dtype = BQQ_BF16), head_dim 128,
+ * at most 16 query heads per kv head; pointers 16-byte aligned, leading dimensions
+ * multiples of 8.  workspace: bqq_attention_decode_workspace_bytes bytes,
+ * 16-byte aligned, zero-filled once before its first use (the kernel leaves its
+ * counters zeroed); one workspace serves one stream.
+ */
+size_t bqq_attention_decode_workspace_bytes(int B, int heads, int kv_heads);
+int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cache, void* v_cache, int64_t ld_cache,
+                         int max_seq, const void* cos_table, const void* sin_table, const int32_t* lens,
+                         int B, int heads, int kv_heads, int head_dim, int dtype, void* out, int64_t ld_out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Diagnostic: issue rate of one instruction kind on the current device, in
  * warp-instructions per SM and clock (at the device's nominal SM clock), measured
  * with CUDA events over one launch of `iters` rounds per warp on 32 warps per SM.
