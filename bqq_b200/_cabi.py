@@ -23,7 +23,7 @@ EXPORTS = [
     'bqq_decode_workspace_bytes', 'bqq_forward_decode', 'bqq_forward_decode_fused',
     'bqq_prefill_workspace_bytes', 'bqq_forward_prefill',
     'bqq_forward_workspace_bytes', 'bqq_forward', 'bqq_reconstruct_weight',
-    'bqq_decode_launches', 'bqq_instruction_rate', 'bqq_attention_decode_workspace_bytes', 'bqq_attention_decode', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
+    'bqq_decode_launches', 'bqq_instruction_rate', 'bqq_attention_decode_workspace_bytes', 'bqq_attention_decode', 'bqq_attention_decode_gathered', 'bqq_forward_host_workspace_bytes', 'bqq_forward_host',
     'bqq_noalloc_scratch_bytes', 'bqq_forward_decode_noalloc', 'bqq_noalloc_status',
     'bqq_decode_status', 'bqq_prefill_status',
     'bqq_peer_region_bytes', 'bqq_peer_alloc', 'bqq_peer_open', 'bqq_peer_close', 'bqq_peer_free',
@@ -92,6 +92,8 @@ def _load():
         'bqq_attention_decode_workspace_bytes': (C.c_size_t, [i32, i32, i32]),
         'bqq_attention_decode': (i32, [vp, i64, vp, vp, i64, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, i64, vp,
                                        C.c_size_t, vp]),
+        'bqq_attention_decode_gathered': (i32, [vp, vp, i64, vp, vp, i64, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp,
+                                                i64, vp, i64, vp, C.c_size_t, vp]),
         'bqq_forward_host_workspace_bytes': (sz, [dp, i32, i32, i32]),
         'bqq_forward_host': (i32, [lp, vp, i32, i32, i64, vp, i32, i64, vp, sz, vp]),
         'bqq_peer_region_bytes': (sz, [sz]),

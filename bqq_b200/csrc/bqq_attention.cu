@@ -11,7 +11,13 @@
 // warp.  The CTA whose range ends at the new position computes the rotated k itself, writes k and v into the cache
 // and into its tile.  Partial results (m, l, 128 numerators) go to scratch; the CTA that draws the last ticket of its
 // (sequence, kv head) adds them in split order and writes bf16 outputs.
+// With a peer gather group (heads sharded over the ranks of one node) the finished output words also go, with the
+// gather's sequence number, into every rank's slot region (the protocol of bqq_peer.cu), and a few more CTAs of the
+// same grid (blockIdx.x >= splits) wait, bounded, for all ranks' words and write the gathered rows.
 #include <cuda_bf16.h>
+#include <string.h>
+
+#include <algorithm>
 
 #include "bqq_common.cuh"
 
@@ -40,13 +46,89 @@ struct AttParams {
   unsigned* tickets;             // [B][kv_heads], zero between launches
   int heads, kv_heads, max_seq, splits;
   float scale;
+  // optional gather of the outputs over the ranks of a peer group (all zero when unused)
+  uint8_t* peer_regions[BQQ_MAX_PEERS];
+  int peer_world, peer_rank;
+  unsigned long long peer_half;  // bytes of one half of a region's slot area
+  long long peer_wait;           // clock budget of one wait on a peer
+  uint32_t* peer_out;            // gathered rows [B][world * heads * 64] words
+  long long peer_ld_out;         // its row pitch in words
 };
+
+// Words w0 (dimensions 4 lane, 4 lane + 1) and w1 (the next two) of query head `head` of sequence b: into slot
+// [b][rank-major column] of every rank's region, each with the sequence number of this gather.
+__device__ __forceinline__ void att_peer_send(const AttParams& p, int b, int head, int lane, uint32_t w0, uint32_t w1) {
+  const unsigned* mine = reinterpret_cast<const unsigned*>(p.peer_regions[p.peer_rank]);
+  const unsigned count = *reinterpret_cast<const volatile unsigned*>(mine) + 1u;
+  const unsigned seq = count | 0x80000000u;
+  const size_t row_words = (size_t)p.heads * (kAttDim / 2);
+  const size_t slot = ((size_t)b * p.peer_world + p.peer_rank) * row_words + (size_t)head * (kAttDim / 2) + 2 * lane;
+  const size_t off = kPeerCtrlBytes + (count & 1u) * p.peer_half + slot * 8;
+  for (int q = 0; q < p.peer_world; ++q) {
+    peer_slot_store(p.peer_regions[q] + off, w0, seq);
+    peer_slot_store(p.peer_regions[q] + off + 8, w1, seq);
+  }
+}
+
+// Receiving CTAs (blockIdx.x >= splits): poll every slot of this rank's region until it carries the gather's sequence
+// number (bounded), write the data words to the gathered rows; the last one to finish advances the gather count.
+__device__ __forceinline__ void att_peer_receive(const AttParams& p) {
+  __shared__ int s_giveup;
+  // the gathered tensor may still be read by earlier kernels of the stream
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int tid = threadIdx.x;
+  if (tid == 0) s_giveup = 0;
+  __syncthreads();
+  unsigned* mine = reinterpret_cast<unsigned*>(p.peer_regions[p.peer_rank]);
+  const unsigned count = *reinterpret_cast<volatile unsigned*>(mine) + 1u;
+  const unsigned e = count | 0x80000000u;
+  const uint8_t* slots = reinterpret_cast<const uint8_t*>(mine) + kPeerCtrlBytes + (count & 1u) * p.peer_half;
+  const long long grow = (long long)p.heads * (kAttDim / 2) * p.peer_world;     // words of one gathered row
+  const long long n = (long long)gridDim.z * grow;
+  const int per_x = (int)gridDim.x - p.splits;
+  const long long receivers = (long long)per_x * gridDim.y * gridDim.z;
+  const long long me = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * per_x + ((int)blockIdx.x - p.splits);
+  for (long long w = me * blockDim.x + tid; w < n; w += receivers * blockDim.x) {
+    uint2 v = peer_slot_load(slots + 8 * w);
+    if (v.y != e) {
+      const long long t0 = clock64();
+      while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
+        if (clock64() - t0 > p.peer_wait) { s_giveup = 1; break; }
+        v = peer_slot_load(slots + 8 * w);
+      }
+    }
+    const long long r = w / grow, c = w - r * grow;
+    p.peer_out[r * p.peer_ld_out + c] = v.x;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    if (s_giveup) atomicExch(mine + 1, 1u);
+    // every word has arrived, so every sender of this rank has read the gather count: the last receiver advances it
+    __threadfence();
+    if (atomicAdd(mine + 2, 1u) == (unsigned)(receivers - 1)) {
+      mine[2] = 0u;
+      *reinterpret_cast<volatile unsigned*>(mine) = count;
+    }
+  }
+}
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// four finished outputs of a lane (dimensions 4 lane .. 4 lane + 3 of one query head): to the local tensor and, with a
+// peer group, to every rank
+__device__ __forceinline__ void att_write(const AttParams& p, int b, int head, int lane, float v0, float v1, float v2, float v3) {
+  const __nv_bfloat162 h0 = __floats2bfloat162_rn(v0, v1), h1 = __floats2bfloat162_rn(v2, v3);
+  __nv_bfloat16* o = p.out + (size_t)b * p.ld_out + (size_t)head * kAttDim + 4 * lane;
+  *reinterpret_cast<__nv_bfloat162*>(o) = h0;
+  *reinterpret_cast<__nv_bfloat162*>(o + 2) = h1;
+  if (p.peer_world)
+    att_peer_send(p, b, head, lane, *reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+}
 
 __global__ void __launch_bounds__(kAttThreads)
 bqq_attention_decode_kernel(const AttParams p) {
@@ -56,6 +138,10 @@ bqq_attention_decode_kernel(const AttParams p) {
   float* sq = reinterpret_cast<float*>(sv + kAttTile * kAttRow);   // [group][128] rotated, scaled q
   __shared__ int s_last;
 
+  if (p.peer_world && (int)blockIdx.x >= p.splits) {
+    att_peer_receive(p);
+    return;
+  }
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = p.heads / p.kv_heads;
@@ -190,9 +276,7 @@ bqq_attention_decode_kernel(const AttParams p) {
       const int g = warp + 4 * s;
       if (g >= group) break;
       const float inv = 1.f / l_run[s];
-      __nv_bfloat16* o = p.out + (size_t)b * p.ld_out + (size_t)(hk * group + g) * kAttDim + 4 * lane;
-      *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(acc[s][0] * inv, acc[s][1] * inv);
-      *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(acc[s][2] * inv, acc[s][3] * inv);
+      att_write(p, b, hk * group + g, lane, acc[s][0] * inv, acc[s][1] * inv, acc[s][2] * inv, acc[s][3] * inv);
     }
     return;
   }
@@ -235,9 +319,7 @@ bqq_attention_decode_kernel(const AttParams p) {
       a0 = fmaf(w, v.x, a0); a1 = fmaf(w, v.y, a1); a2 = fmaf(w, v.z, a2); a3 = fmaf(w, v.w, a3);
     }
     const float inv = 1.f / l;
-    __nv_bfloat16* o = p.out + (size_t)b * p.ld_out + (size_t)(hk * group + g) * kAttDim + 4 * lane;
-    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
-    *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(a2 * inv, a3 * inv);
+    att_write(p, b, hk * group + g, lane, a0 * inv, a1 * inv, a2 * inv, a3 * inv);
   }
 }
 
@@ -260,10 +342,11 @@ extern "C" size_t bqq_attention_decode_workspace_bytes(int B, int heads, int kv_
   return 256 * (((size_t)B * kv_heads * sizeof(unsigned) + 255) / 256) + att_partial_bytes(B, heads);
 }
 
-extern "C" int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cache, void* v_cache, int64_t ld_cache,
-                                    int max_seq, const void* cos_table, const void* sin_table, const int32_t* lens,
-                                    int B, int heads, int kv_heads, int head_dim, int dtype, void* out, int64_t ld_out,
-                                    void* workspace, size_t workspace_bytes, void* stream) {
+static int attention_launch(const void* qkv, int64_t ld_qkv, void* k_cache, void* v_cache, int64_t ld_cache,
+                            int max_seq, const void* cos_table, const void* sin_table, const int32_t* lens,
+                            int B, int heads, int kv_heads, int head_dim, int dtype, void* out, int64_t ld_out,
+                            void* workspace, size_t workspace_bytes, void* stream, const BqqPeerGroup* peer,
+                            void* gathered, int64_t ld_gathered) {
   using namespace bqq;
   if (!qkv || !k_cache || !v_cache || !cos_table || !sin_table || !lens || !out || !workspace) return BQQ_ERR_NULL;
   if (B < 1 || heads < 1 || kv_heads < 1 || max_seq < 1 || heads % kv_heads != 0) return BQQ_ERR_BAD_SHAPE;
@@ -273,6 +356,7 @@ extern "C" int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cac
   if (((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out | (uintptr_t)workspace) & 15) return BQQ_ERR_MISALIGNED;
   if ((ld_qkv | ld_cache | ld_out) & 7) return BQQ_ERR_MISALIGNED;
   AttParams p;
+  memset(&p, 0, sizeof(p));
   p.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
   p.ld_qkv = ld_qkv;
   p.kc = reinterpret_cast<__nv_bfloat16*>(k_cache);
@@ -288,6 +372,29 @@ extern "C" int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cac
   p.heads = heads; p.kv_heads = kv_heads; p.max_seq = max_seq;
   p.splits = att_splits(B, kv_heads, max_seq);
   p.scale = 1.f / sqrtf((float)head_dim);
+  int recv_x = 0;
+  if (peer) {
+    if (!gathered) return BQQ_ERR_NULL;
+    if (peer->world < 1 || peer->world > BQQ_MAX_PEERS || peer->rank < 0 || peer->rank >= peer->world) return BQQ_ERR_BAD_SHAPE;
+    const size_t row_bytes = (size_t)heads * kAttDim * 2;
+    if ((size_t)B * row_bytes * peer->world > peer->gather_bytes) return BQQ_ERR_WORKSPACE;
+    if (ld_gathered < (int64_t)heads * kAttDim * peer->world) return BQQ_ERR_BAD_SHAPE;
+    if (((uintptr_t)gathered & 3) || (ld_gathered & 1)) return BQQ_ERR_MISALIGNED;
+    for (int q = 0; q < peer->world; ++q) {
+      if (!peer->regions[q]) return BQQ_ERR_NULL;
+      p.peer_regions[q] = reinterpret_cast<uint8_t*>(peer->regions[q]);
+    }
+    p.peer_world = peer->world;
+    p.peer_rank = peer->rank;
+    p.peer_half = peer_half_bytes(peer->gather_bytes);
+    p.peer_wait = peer->wait_cycles ? (long long)peer->wait_cycles : 2000000000LL;
+    p.peer_out = reinterpret_cast<uint32_t*>(gathered);
+    p.peer_ld_out = ld_gathered / 2;
+    // receiving CTAs: about one thread per four words of the gathered rows, spread over the (kv head, sequence) columns
+    const long long words = (long long)B * heads * (kAttDim / 2) * peer->world;
+    const long long cols = (long long)kv_heads * B;
+    recv_x = (int)std::min<long long>(8, std::max<long long>(1, (words / 4 + kAttThreads * cols - 1) / (kAttThreads * cols)));
+  }
   const size_t smem = (size_t)2 * kAttTile * kAttRow + (size_t)(heads / kv_heads) * kAttDim * sizeof(float);
   if (cudaFuncSetAttribute(bqq_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();
@@ -297,7 +404,7 @@ extern "C" int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cac
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.splits, kv_heads, B);
+  cfg.gridDim = dim3(p.splits + recv_x, kv_heads, B);
   cfg.blockDim = dim3(kAttThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = reinterpret_cast<cudaStream_t>(stream);
@@ -305,4 +412,22 @@ extern "C" int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cac
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, bqq_attention_decode_kernel, p) != cudaSuccess) { cudaGetLastError(); return BQQ_ERR_CUDA; }
   return launch_status();
+}
+
+extern "C" int bqq_attention_decode(const void* qkv, int64_t ld_qkv, void* k_cache, void* v_cache, int64_t ld_cache,
+                                    int max_seq, const void* cos_table, const void* sin_table, const int32_t* lens,
+                                    int B, int heads, int kv_heads, int head_dim, int dtype, void* out, int64_t ld_out,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  return attention_launch(qkv, ld_qkv, k_cache, v_cache, ld_cache, max_seq, cos_table, sin_table, lens, B, heads, kv_heads,
+                          head_dim, dtype, out, ld_out, workspace, workspace_bytes, stream, nullptr, nullptr, 0);
+}
+
+extern "C" int bqq_attention_decode_gathered(const BqqPeerGroup* group, const void* qkv, int64_t ld_qkv, void* k_cache,
+                                             void* v_cache, int64_t ld_cache, int max_seq, const void* cos_table,
+                                             const void* sin_table, const int32_t* lens, int B, int heads, int kv_heads,
+                                             int head_dim, int dtype, void* out_local, int64_t ld_out, void* gathered,
+                                             int64_t ld_gathered, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!group) return BQQ_ERR_NULL;
+  return attention_launch(qkv, ld_qkv, k_cache, v_cache, ld_cache, max_seq, cos_table, sin_table, lens, B, heads, kv_heads,
+                          head_dim, dtype, out_local, ld_out, workspace, workspace_bytes, stream, group, gathered, ld_gathered);
 }

@@ -36,10 +36,12 @@ from .sharded import gather_columns
 _ATT_WS: dict = {}
 
 
-def attention_decode(qkv, k_cache, v_cache, cos, sin, lens, heads, kv_heads):
+def attention_decode(qkv, k_cache, v_cache, cos, sin, lens, heads, kv_heads, peer=None):
     """Attention of one new token per sequence with this library's kernel (bqq_attention_decode): rotary embedding
     of q and k at position lens[b], append of k and v to the caches, softmax(q K^T / sqrt(d)) V over the cached
     rows.  qkv [B, 1, heads + 2 kv_heads, 128] bf16, caches [B, max_seq, kv_heads, 128]; returns [B, 1, heads, 128].
+    With `peer` (a PeerGatherGroup; heads and kv_heads are this rank's) the outputs of all ranks are gathered in the
+    same launch and [B, 1, world * heads, 128] is returned, the ranks' heads in rank order.
     Returns None where the kernel does not apply (other types or head sizes), so the caller can take another route."""
     from . import _cabi
     B, T, H, hd = qkv.shape
@@ -55,6 +57,14 @@ def attention_decode(qkv, k_cache, v_cache, cos, sin, lens, heads, kv_heads):
     if ws is None:
         ws = _ATT_WS[key] = torch.zeros(need, dtype=torch.uint8, device=qkv.device)
     out = torch.empty((B, 1, heads, hd), dtype=qkv.dtype, device=qkv.device)
+    if peer is not None:
+        gathered = torch.empty((B, 1, peer.world * heads, hd), dtype=qkv.dtype, device=qkv.device)
+        _cabi.check(_cabi.lib.bqq_attention_decode_gathered(
+            peer.descriptor(), qkv.data_ptr(), qkv.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0),
+            k_cache.shape[1], cos.data_ptr(), sin.data_ptr(), lens.data_ptr(), B, heads, kv_heads, hd, _cabi.BF16,
+            out.data_ptr(), out.stride(0), gathered.data_ptr(), gathered.stride(0), ws.data_ptr(), ws.numel(),
+            stream.cuda_stream), 'bqq_attention_decode_gathered')
+        return gathered
     _cabi.check(_cabi.lib.bqq_attention_decode(qkv.data_ptr(), qkv.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
                                                k_cache.stride(0), k_cache.shape[1], cos.data_ptr(), sin.data_ptr(),
                                                lens.data_ptr(), B, heads, kv_heads, hd, _cabi.BF16, out.data_ptr(),
@@ -154,9 +164,12 @@ class DecoderLayer(nn.Module):
         lh, lkv = self.local_heads, self.local_kv
         # normalisation, SwiGLU and residual adds are folded into the layers' kernels (forward_fused)
         qkv = self.qkv_proj.forward_fused(x, rms_weight=self.norm1, eps=1e-5).view(B, T, lh + 2 * lkv, hd)
-        att = None
+        att, gathered = None, False
         if fa is not None and T == 1 and cfg.own_attention:
-            att = attention_decode(qkv, k_cache, v_cache, fa[0], fa[1], fa[2], lh, lkv)
+            # with several ranks the kernel also gathers its outputs (no separate gather launch)
+            by_peer = self.world > 1 and self._fits(B, lh * hd, x.element_size())
+            att = attention_decode(qkv, k_cache, v_cache, fa[0], fa[1], fa[2], lh, lkv, peer=self.peer if by_peer else None)
+            gathered = att is not None and by_peer
         if att is not None:
             pass
         elif fa is not None and _flash_kvcache is not None and x.dtype in (torch.bfloat16, torch.float16):
@@ -180,7 +193,10 @@ class DecoderLayer(nn.Module):
                 att = F.scaled_dot_product_attention(q, k_cache.transpose(1, 2), v_cache.transpose(1, 2),
                                                      attn_mask=mask, enable_gqa=True)
             att = att.transpose(1, 2)
-        att = self._gather(att.reshape(B, T, self.local_heads * hd))                      # gather 1
+        if gathered:
+            att = att.reshape(B, T, self.world * self.local_heads * hd)                   # gather 1: inside the attention launch
+        else:
+            att = self._gather(att.reshape(B, T, self.local_heads * hd))                  # gather 1
         if self.world == 1:
             x = self.o_proj.forward_fused(att, residual=x)
             gu = self.gate_up_proj.forward_fused(x, rms_weight=self.norm2, eps=1e-5)

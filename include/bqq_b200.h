@@ -381,6 +381,23 @@ int bqq_forward_decode_gathered(const BqqLayer* layer, const void* x, int x_dtyp
                                 void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * bqq_attention_decode for heads sharded over the ranks of a peer group, with the
+ * gather of the outputs in the same launch: every rank passes its local heads
+ * (qkv, caches, out_local as in bqq_attention_decode, `heads` and `kv_heads` being
+ * the local counts) and receives gathered [B][world * heads][head_dim] (ld_gathered
+ * elements between sequences), the ranks' heads side by side in rank order.  The
+ * finished output words are stored into every rank's slot region as they are
+ * produced; a few more CTAs of the same grid wait (bounded) for all ranks' words.
+ * Same rules as bqq_peer_gather: all ranks call in the same order on their streams,
+ * B * world * heads * head_dim * 2 <= gather_bytes.  No counterpart in the reference.
+ */
+int bqq_attention_decode_gathered(const BqqPeerGroup* group, const void* qkv, int64_t ld_qkv, void* k_cache,
+                                  void* v_cache, int64_t ld_cache, int max_seq, const void* cos_table,
+                                  const void* sin_table, const int32_t* lens, int B, int heads, int kv_heads,
+                                  int head_dim, int dtype, void* out_local, int64_t ld_out, void* gathered,
+                                  int64_t ld_gathered, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Dense weight W [rw*P, cw*Q] row-major in element type w_dtype: the value of
  * BinaryQuadratic.get_weight (src/bqq_modules.py:48-55).  Replaces
  * reconstruct_W_kernel (src/bqq_cuda.cu:198-246): the per-entry counts

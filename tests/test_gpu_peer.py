@@ -106,6 +106,31 @@ def _worker(rank, world, port, result_dir):
             want = full(Xd)
             got = shard.forward_gathered(Xd, grp, out_segments=2)
             assert torch.equal(got, want), (rank, 'two segments')
+        # single-token attention with heads sharded over the ranks: the gathered launch returns every rank's heads,
+        # bit for bit what each rank's own launch computes (all ranks' inputs come from seeds, so this rank can
+        # compute the others' heads itself)
+        from bqq_b200.decoder_stack import attention_decode
+        hd, max_seq, lh, lkv = 128, 96, 4, 1
+        ang = torch.arange(max_seq).float()[:, None] * (1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd)))[None, :]
+        cos, sin = ang.cos().to(torch.bfloat16).to(dev), ang.sin().to(torch.bfloat16).to(dev)
+
+        def inputs(q, B):
+            g = torch.Generator().manual_seed(900 + q)
+            return (torch.randn(B, 1, lh + 2 * lkv, hd, generator=g).to(torch.bfloat16).to(dev),
+                    torch.randn(B, max_seq, lkv, hd, generator=g).to(torch.bfloat16).to(dev),
+                    torch.randn(B, max_seq, lkv, hd, generator=g).to(torch.bfloat16).to(dev))
+        for B, pos in ((1, 0), (2, 70), (1, 95)):
+            lens = torch.full((B,), pos, dtype=torch.int32, device=dev)
+            want = []
+            for q in range(world):
+                qkv, kc, vc = inputs(q, B)
+                want.append(attention_decode(qkv, kc, vc, cos, sin, lens, lh, lkv))
+            want = torch.cat(want, dim=2)
+            for _ in range(2):
+                qkv, kc, vc = inputs(rank, B)
+                got = attention_decode(qkv, kc, vc, cos, sin, lens, lh, lkv, peer=grp)
+                torch.cuda.synchronize()
+                assert got.shape == (B, 1, world * lh, hd) and torch.equal(got, want), (rank, 'attention', B, pos)
         grp.status()
         grp.close()
         with open(os.path.join(result_dir, f'ok{rank}'), 'w') as f:
