@@ -571,68 +571,78 @@ def extra_large_layer(device, rank, world, peer_factory, stream):
     return out
 
 
-def extra_stack(device, rank, world, peer_factory, new_tokens=128, prompt=512, batch=1):
+def extra_stack(device, rank, world, peer_factory, new_tokens=128, prompt=512, batches=(1, 8)):
     """Decoder stack (32 layers, hidden 4096, intermediate 14336, 32/8 heads, vocabulary 128256, 2 bit layers,
-    P=Q=r=32): 512-token prompt, 128 greedy tokens at batch 1, decode step replayed from a CUDA graph; layers
-    sharded over the ranks (strong scaling)."""
+    P=Q=r=32): 512-token prompts, 128 greedy tokens at batch 1 (the headline of this object) and batch 8, decode step
+    replayed from a CUDA graph; layers sharded over the ranks (strong scaling)."""
     import torch
     import torch.distributed as dist
     from bqq_b200.decoder_stack import DecoderStack, StackConfig
     cfg = StackConfig(max_seq=prompt + new_tokens)
-    peer = peer_factory(batch * max(cfg.intermediate, cfg.hidden, cfg.vocab) * 2) if world > 1 else None
+    peer = peer_factory(max(batches) * max(cfg.intermediate, cfg.hidden, cfg.vocab) * 2) if world > 1 else None
     model = DecoderStack(cfg, device, seed=0, rank=rank, world=world, peer=peer)
-    gen = torch.Generator(device=device).manual_seed(1)
-    ids0 = torch.randint(0, cfg.vocab, (batch, prompt), generator=gen, device=device)
-    cache = model.new_cache(batch)
     stream = torch.cuda.Stream(device)
-    with torch.cuda.stream(stream):
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        ids = model.prefill(ids0, cache)
-        pos = torch.full((1,), prompt, device=device, dtype=torch.int64)
-        static_ids = ids.clone()
-        model.decode_step(static_ids, cache, pos)
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            nxt = model.decode_step(static_ids, cache, pos)
-            static_ids.copy_(nxt)
-            pos.add_(1)
-        best_decode = best_prefill = None
-        for _ in range(3):
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0.record(stream)
-            ids = model.prefill(ids0, cache)
-            e1.record(stream)
-            static_ids.copy_(ids)
-            pos.fill_(prompt)
-            for _ in range(new_tokens - 1):
-                graph.replay()
-            e2.record(stream)
-            stream.synchronize()
-            pre, dec = e0.elapsed_time(e1), e1.elapsed_time(e2)
-            best_prefill = pre if best_prefill is None else min(best_prefill, pre)
-            best_decode = dec if best_decode is None else min(best_decode, dec)
-    if world > 1:
-        t = torch.tensor([best_decode, best_prefill], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        best_decode, best_prefill = t.tolist()
     steps = new_tokens - 1
-    res = {'tokens_per_s': batch * steps / (best_decode * 1e-3), 'ms_per_step': best_decode / steps, 'batch': batch,
+    runs = {}
+    for batch in batches:
+        gen = torch.Generator(device=device).manual_seed(1)
+        ids0 = torch.randint(0, cfg.vocab, (batch, prompt), generator=gen, device=device)
+        cache = model.new_cache(batch)
+        with torch.cuda.stream(stream):
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            ids = model.prefill(ids0, cache)
+            pos = torch.full((1,), prompt, device=device, dtype=torch.int64)
+            static_ids = ids.clone()
+            model.decode_step(static_ids, cache, pos)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                nxt = model.decode_step(static_ids, cache, pos)
+                static_ids.copy_(nxt)
+                pos.add_(1)
+            best_decode = best_prefill = None
+            for _ in range(3 if batch == 1 else 2):
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                e0.record(stream)
+                ids = model.prefill(ids0, cache)
+                e1.record(stream)
+                static_ids.copy_(ids)
+                pos.fill_(prompt)
+                for _ in range(steps):
+                    graph.replay()
+                e2.record(stream)
+                stream.synchronize()
+                pre, dec = e0.elapsed_time(e1), e1.elapsed_time(e2)
+                best_prefill = pre if best_prefill is None else min(best_prefill, pre)
+                best_decode = dec if best_decode is None else min(best_decode, dec)
+            graph.reset()
+        if world > 1:
+            t = torch.tensor([best_decode, best_prefill], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            best_decode, best_prefill = t.tolist()
+        runs[batch] = {'tokens_per_s': batch * steps / (best_decode * 1e-3), 'ms_per_step': best_decode / steps,
+                       'prefill_ms': best_prefill}
+        del cache, graph
+        torch.cuda.empty_cache()
+    first = batches[0]
+    res = {'tokens_per_s': runs[first]['tokens_per_s'], 'ms_per_step': runs[first]['ms_per_step'], 'batch': first,
            'layers': cfg.layers, 'scaling': 'strong', 'prompt': prompt, 'new_tokens': new_tokens,
-           'prefill_ms': best_prefill, 'bqq_bytes_per_token_per_gpu': model.bqq_bytes_per_token(),
+           'prefill_ms': runs[first]['prefill_ms'], 'bqq_bytes_per_token_per_gpu': model.bqq_bytes_per_token(),
            'gathers': 'none' if world == 1 else 'peer stores', 'lm_head': 'dense bf16, included',
-           'attention': 'decode steps: bqq_attention_decode of this library (rotary embedding, cache append and '
-                        'attention in one launch); prefill: flash_attn library call',
+           'attention': 'decode steps: bqq_attention_decode of this library (rotary embedding, cache append, attention '
+                        'and, with several ranks, the gather of its outputs in one launch); prefill: flash_attn '
+                        'library call',
            'coefficients': 'N(0, 0.02/sqrt(in/4096)) for a, 0.05 of that for b, c, d (keeps activations finite '
                            'through 32 random layers; speed does not depend on the values)'}
-    graph.reset()
+    for batch in batches[1:]:
+        res[f'batch{batch}'] = runs[batch]
     torch.cuda.synchronize()
     if peer is not None:
         peer.status()
         peer.close()
-    del model, cache
+    del model
     torch.cuda.empty_cache()
     return res
 
