@@ -89,17 +89,29 @@ __device__ __forceinline__ void att_peer_receive(const AttParams& p) {
   const int per_x = (int)gridDim.x - p.splits;
   const long long receivers = (long long)per_x * gridDim.y * gridDim.z;
   const long long me = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * per_x + ((int)blockIdx.x - p.splits);
-  for (long long w = me * blockDim.x + tid; w < n; w += receivers * blockDim.x) {
-    uint2 v = peer_slot_load(slots + 8 * w);
-    if (v.y != e) {
-      const long long t0 = clock64();
-      while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
-        if (clock64() - t0 > p.peer_wait) { s_giveup = 1; break; }
-        v = peer_slot_load(slots + 8 * w);
-      }
+  // four slots per round, their loads in flight together; a slot that has not arrived yet is polled on its own
+  const long long step = receivers * blockDim.x;
+  for (long long w0 = me * blockDim.x + tid; w0 < n; w0 += 4 * step) {
+    uint2 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long w = w0 + k * step;
+      v[k] = w < n ? peer_slot_load(slots + 8 * w) : make_uint2(0u, e);
     }
-    const long long r = w / grow, c = w - r * grow;
-    p.peer_out[r * p.peer_ld_out + c] = v.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long w = w0 + k * step;
+      if (w >= n) break;
+      if (v[k].y != e) {
+        const long long t0 = clock64();
+        while (v[k].y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
+          if (clock64() - t0 > p.peer_wait) { s_giveup = 1; break; }
+          v[k] = peer_slot_load(slots + 8 * w);
+        }
+      }
+      const long long r = w / grow, c = w - r * grow;
+      p.peer_out[r * p.peer_ld_out + c] = v[k].x;
+    }
   }
   __syncthreads();
   if (tid == 0) {
@@ -390,10 +402,10 @@ static int attention_launch(const void* qkv, int64_t ld_qkv, void* k_cache, void
     p.peer_wait = peer->wait_cycles ? (long long)peer->wait_cycles : 2000000000LL;
     p.peer_out = reinterpret_cast<uint32_t*>(gathered);
     p.peer_ld_out = ld_gathered / 2;
-    // receiving CTAs: about one thread per four words of the gathered rows, spread over the (kv head, sequence) columns
+    // receiving CTAs: about one thread per two words of the gathered rows, spread over the (kv head, sequence) columns
     const long long words = (long long)B * heads * (kAttDim / 2) * peer->world;
     const long long cols = (long long)kv_heads * B;
-    recv_x = (int)std::min<long long>(8, std::max<long long>(1, (words / 4 + kAttThreads * cols - 1) / (kAttThreads * cols)));
+    recv_x = (int)std::min<long long>(8, std::max<long long>(1, (words / 2 + kAttThreads * cols - 1) / (kAttThreads * cols)));
   }
   const size_t smem = (size_t)2 * kAttTile * kAttRow + (size_t)(heads / kv_heads) * kAttDim * sizeof(float);
   if (cudaFuncSetAttribute(bqq_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

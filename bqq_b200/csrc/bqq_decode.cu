@@ -154,7 +154,8 @@ int decode_launch(const BqqLayer* L, const void* x, int x_dtype, int M, int64_t 
     p.peer_wait = peer->wait_cycles ? (long long)peer->wait_cycles : 2000000000LL;
     const long long words = (long long)M * p.peer_row_words * peer->world;
     const int threads = kDT * pl.bpc;
-    pl.nrecv = (int)std::min<long long>(8, std::max<long long>(1, (words + 2 * threads - 1) / (2 * threads)));
+    // receiving CTAs: about two words per thread, at most 32 CTAs
+    pl.nrecv = (int)std::min<long long>(32, std::max<long long>(1, (words + 2 * threads - 1) / (2 * threads)));
   }
   switch (pl.variant) {
     case 0: return decode_launch_variant<0>(p, pl, st);

@@ -427,17 +427,29 @@ __device__ __forceinline__ void peer_receive(const DecodeParams& p) {
     const long long grow = (long long)p.peer_row_words * p.peer_world;
     const long long n = (long long)p.M * grow;
     const long long step = (long long)(gridDim.x - p.ncompute) * blockDim.x;
-    for (long long w = (long long)(blockIdx.x - p.ncompute) * blockDim.x + tid; w < n; w += step) {
-      uint2 v = peer_slot_load(slots + 8 * w);
-      if (v.y != e) {
-        const long long t0 = clock64();
-        while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
-          if (clock64() - t0 > p.peer_wait) { s_giveup = 1; break; }
-          v = peer_slot_load(slots + 8 * w);
-        }
+    // four slots per round: their loads are in flight together, so a thread that owns many words does not pay one
+    // L2 round trip per word; a slot that has not arrived yet is polled (bounded) on its own
+    for (long long w0 = (long long)(blockIdx.x - p.ncompute) * blockDim.x + tid; w0 < n; w0 += 4 * step) {
+      uint2 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const long long w = w0 + k * step;
+        v[k] = w < n ? peer_slot_load(slots + 8 * w) : make_uint2(0u, e);
       }
-      const long long r = w / grow, c = w - r * grow;
-      p.peer_out[r * p.peer_ld_out + c] = v.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const long long w = w0 + k * step;
+        if (w >= n) break;
+        if (v[k].y != e) {
+          const long long t0 = clock64();
+          while (v[k].y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
+            if (clock64() - t0 > p.peer_wait) { s_giveup = 1; break; }
+            v[k] = peer_slot_load(slots + 8 * w);
+          }
+        }
+        const long long r = w / grow, c = w - r * grow;
+        p.peer_out[r * p.peer_ld_out + c] = v[k].x;
+      }
     }
   }
   __syncthreads();

@@ -83,18 +83,29 @@ bqq_peer_gather_kernel(const PeerArgs a) {
   // receive: poll every slot of my region
   const uint2* slots = reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(mine) + kPeerCtrlBytes + half);
   const long long nrecv = (long long)a.rows * grow;
-  for (long long w = gtid; w < nrecv; w += gthreads) {
-    uint2 v = ld_slot(slots + w);
-    if (v.y != e) {
-      const long long t0 = clock64();
-      while (v.y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
-        if (clock64() - t0 > a.wait_cycles) { s_giveup = 1; break; }
-        __nanosleep(32);
-        v = ld_slot(slots + w);
-      }
+  // four slots per round, their loads in flight together; a slot that has not arrived yet is polled on its own
+  for (long long w0 = gtid; w0 < nrecv; w0 += 4 * gthreads) {
+    uint2 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long w = w0 + k * gthreads;
+      v[k] = w < nrecv ? ld_slot(slots + w) : make_uint2(0u, e);
     }
-    const long long r = w / grow, c = w - r * grow;
-    a.out[r * a.ld_out + c] = v.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long w = w0 + k * gthreads;
+      if (w >= nrecv) break;
+      if (v[k].y != e) {
+        const long long t0 = clock64();
+        while (v[k].y != e && !*reinterpret_cast<volatile int*>(&s_giveup)) {
+          if (clock64() - t0 > a.wait_cycles) { s_giveup = 1; break; }
+          __nanosleep(32);
+          v[k] = ld_slot(slots + w);
+        }
+      }
+      const long long r = w / grow, c = w - r * grow;
+      a.out[r * a.ld_out + c] = v[k].x;
+    }
   }
   __syncthreads();
   // every slot has arrived, so a sending producer has issued all its stores; it must also have ended
