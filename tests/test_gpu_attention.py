@@ -30,16 +30,18 @@ def _reference(qkv, kc, vc, cos, sin, lens, heads, kv):
     return out, kc, vc
 
 
-@pytest.mark.parametrize('B,heads,kv,positions', [
-    (1, 32, 8, [0, 5, 63, 64, 200, 639]),        # the stack on one GPU: 18 splits
-    (2, 4, 1, [0, 31, 300]),                      # a shard of it (heads / 8), two sequences: 32 splits
-    (1, 8, 8, [7, 130]),                          # one query head per kv head
-    (3, 64, 4, [1, 100]),                         # 16 query heads per kv head (four per warp)
+@pytest.mark.parametrize('B,heads,kv,positions,max_seq', [
+    (1, 32, 8, [0, 5, 63, 64, 200, 639], 640),   # the stack on one GPU: 20 splits of at most 32 keys
+    (2, 4, 1, [0, 31, 300], 640),                 # a shard of it (heads / 8), two sequences
+    (1, 8, 8, [7, 130], 640),                     # one query head per kv head
+    (3, 64, 4, [1, 100], 640),                    # 16 query heads per kv head (four per warp)
+    (2, 8, 2, [0, 17, 31], 32),                   # short cache: one split, outputs written without the combination
+    (1, 32, 8, [70, 2047, 4000, 4095], 4096),     # long cache: 32 splits of up to 128 keys, several tiles per CTA
 ])
-def test_attention_decode_matches_torch(B, heads, kv, positions):
+def test_attention_decode_matches_torch(B, heads, kv, positions, max_seq):
     from bqq_b200.decoder_stack import attention_decode
     dev = torch.device('cuda')
-    hd, max_seq = 128, 640
+    hd = 128
     g = torch.Generator(device=dev).manual_seed(5)
     inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device=dev).float() / hd))
     ang = torch.arange(max_seq, device=dev).float()[:, None] * inv[None, :]
